@@ -41,7 +41,8 @@ enum {
   PIEH_EPI_RELU2 = 1,    /* y <- max(y, 0)^2                                   */
   PIEH_EPI_SOFTCAP = 2,  /* y <- cap * tanh(y / cap)                           */
   PIEH_EPI_STREAMS = 3,  /* out is the residual [M, S, N] fp32: x[m, t, n] <- sum_s mix[s, t] x[m, s, n] + outw[t] * y */
-  PIEH_EPI_GLU = 4       /* gated pair (pieh_linear_glu only): out [M, N / 2]                                        */
+  PIEH_EPI_GLU = 4,      /* gated pair (pieh_linear_glu only): out [M, N / 2]                                        */
+  PIEH_EPI_SIGMUL = 5    /* y <- y * sigmoid(gate[m, n])   (pieh_linear_batched only)                                */
 };
 
 /* ragged step descriptor, shared by the recurrent and the attention operators (all arrays int32, device) */
@@ -67,6 +68,14 @@ typedef struct pieh_batch {
 int pieh_linear(void* out, int out_dtype, long long out_ld, const void* x, int x_dtype, long long x_ld, const void* w,
                 int w_dtype, const float* bias, int M, int N, int K, int epilogue, float epi_a, const float* mix,
                 const float* outw, int S, void* stream);
+
+/* nb independent products in one launch (one per head, say): for z < nb
+ *   out[z * out_bs + m * out_ld + n] = sum_k x[z * x_bs + m * x_ld + k] * w[z * w_bs + n * K + k]
+ * (strides in elements), with the same dtype rules as pieh_linear.  epilogue NONE, RELU2 or SIGMUL; SIGMUL multiplies by
+ * sigmoid(gate[z * gate_bs + m * gate_ld + n]), gate fp32 logits. */
+int pieh_linear_batched(void* out, int out_dtype, long long out_ld, long long out_bs, const void* x, int x_dtype,
+                        long long x_ld, long long x_bs, const void* w, int w_dtype, long long w_bs, int nb, int M, int N,
+                        int K, int epilogue, const float* gate, long long gate_ld, long long gate_bs, void* stream);
 
 /* xs[t, s, :] = table[tokens[t], :] for every stream s.  xs fp32 [T, S, W]. */
 int pieh_embed_streams(float* xs, const void* table, int table_dtype, const int32_t* tokens, int T, int S, int W,
@@ -178,11 +187,22 @@ typedef struct pieh_bias_attn {
   void* k_pages;           /* [pages, 64, G, d]  act dtype */
   void* v_pages;           /* [pages, 64, G, dv] act dtype */
   int kv_dtype;
+  /* optional pieces (all zero / NULL: off) */
+  const float* sinks;      /* [H] learned sink logits: the denominator gains exp(sinks[h]) (unscaled, once) instead of the
+                              score-0 term of `sink` */
+  int gate_heads;          /* 1: the gate at g_off holds ONE logit per head ([H]) instead of one per output feature */
+  int rot_dims;            /* leading features of every query / key head that rotate, feature i paired with i + rot_dims / 2 */
+  const float* rot_cs;     /* [T, rot_dims / 2, 2] (cos, sin) of each row's angles: pieh_rot_table */
+  const float* v_mix;      /* device scalar lambda: v <- (1 - lambda) v + lambda v_keep[t] before the pages are written */
+  float* v_keep;           /* [T, G dv] fp32: read when v_mix is set; otherwise, if not NULL, this call's values are left here */
 } pieh_bias_attn;
-/* q_out fp32 [T, H, d]; k' and v appended to the pages at each row's position. */
+/* q_out fp32 [T, H, d]; k' and v appended to the pages at each row's position.  Rotation (after the norms) turns the pair
+ * (u, v) = (x[i], x[i + rot_dims / 2]) into (u cos - v sin, v cos + u sin). */
 int pieh_bias_attn_prepare(float* q_out, const float* proj, long long ld, const pieh_bias_attn* a, const pieh_batch* b,
                            void* stream);
-/* out act [T, H dv]; proj is read for the gate. */
+/* cs[t, i] = (cos, sin)(positions[t] * freqs[i]), the angle formed in double precision.  cs fp32 [T, half, 2]. */
+int pieh_rot_table(float* cs, const int32_t* positions, const double* freqs, int T, int half, void* stream);
+/* out act [T, H dv]; proj is read for the gate.  dv <= 512. */
 int pieh_bias_attn_run(void* out, int out_dtype, const float* q, const float* proj, long long ld,
                        const pieh_bias_attn* a, const pieh_batch* b, void* stream);
 
@@ -204,13 +224,54 @@ typedef struct pieh_moe_plan {
   int32_t* tiles64;      /* [1 + 3 * (T * top / 64 + E)]  */
   int32_t* tiles128;     /* [1 + 3 * (T * top / 128 + E)] */
   int32_t* counters;     /* [2 * E + 2] scratch */
+  int softmax_top;       /* 1: no groups, no sigmoid: the `top` largest LOGITS are chosen and weigh softmax over the chosen
+                            logits only (times scale) */
 } pieh_moe_plan;
 int pieh_moe_route(const float* z, long long ld, const pieh_moe_plan* p, int T, void* stream);
 /* Grouped product over the slots: out[s, :] = x[row(s), :] W_e(s)^T with W_e = w + e * w_stride elements, row(s) =
- * slot_row[s] when gather_rows else s.  P = T * top slots.  glu: as pieh_linear_glu (silu when alpha 1, limit 0). */
+ * slot_row[s] when gather_rows else s.  P = T * top slots.  glu 1: as pieh_linear_glu (silu when alpha 1, limit 0);
+ * glu 2: no pair, out = max(y, 0)^2;  glu 0: plain. */
 int pieh_moe_linear(void* out, int out_dtype, long long out_ld, const void* x, int x_dtype, long long x_ld, const void* w,
                     int w_dtype, long long w_stride, int P, int N, int K, int gather_rows, int glu, float alpha,
                     float limit, float up_offset, const pieh_moe_plan* p, void* stream);
+
+/* ---- parallel pre-norm blocks with a causal input convolution ------------------------------------------------------
+ * x[t, :] = table[tokens[t], :] * scale   (fp32 residual) */
+int pieh_embed_scaled(float* x, const void* table, int table_dtype, const int32_t* tokens, float scale, int T, int W,
+                      int vocab, void* stream);
+/* The residual takes a block's output and the NEXT block's norm is formed in the same pass:
+ *   x[t, :] += (y ? y[t, :] : 0) + (mix ? mixture as in pieh_postnorm_add : 0)      (a NULL shared_gate: the shared rows count fully)
+ *   h[t, :]  = x[t, :] / sqrt(mean(x[t, :]^2) + eps) * norm_w                          (skipped when h or norm_w is NULL)
+ * x, h fp32 [T, W]. */
+int pieh_residual_norm(float* x, const float* y, const pieh_mix_sum* mix, float* h, const float* norm_w, float eps, int T,
+                       int W, void* stream);
+/* Causal convolution over time on every channel, added to its input, for up to 4 tap sets that read the same h:
+ *   out_k[t, c] = h[t, c] + sum_j w_k[c, j] * h[t - taps + 1 + j, c]        (rows before the sequence's start are zero)
+ * The last taps - 1 rows of h of every sequence are its state (fp32, oldest first, in the sequence's slot); the call reads
+ * the state for rows that reach back before the step and then moves it on. */
+typedef struct pieh_canon {
+  int taps, n_out;
+  const float* w[4];   /* [W, taps] fp32 each */
+  void* out[4];        /* act [T, W] each */
+  float* state;        /* [slots, taps - 1, W] fp32 (unused when taps == 1) */
+} pieh_canon;
+int pieh_canon_conv(const pieh_canon* c, int out_dtype, const float* h, int W, const pieh_batch* b, void* stream);
+
+/* ---- minGRU: a gated recurrence whose gates read the current token only ------------------------------------------------
+ * proj fp32 [T, ld]: columns [z logits | u | gate], `width` each.  z = sigmoid(.), candidate = u + 1/2 (u >= 0) or
+ * sigmoid(u) (u < 0), S_t = (1 - z) S_(t-1) + z candidate per channel, out[t, :] = S_t * silu(gate).  state fp32
+ * [slots, width]: read unless the sequence has no context, written back at the end. */
+int pieh_mingru_scan(void* out, int out_dtype, const float* proj, long long ld, int width, float* state,
+                     const pieh_batch* b, void* stream);
+
+/* ---- latent attention: the cached latent and the query latent ------------------------------------------------------------
+ * proj fp32 [T, ld]: the query latent at column 0 (q_rank) and the key / value latent at kv_off (kv_rank).  Both get an
+ * RMS norm with a plain weight; the query latent goes to cq_out (act [T, q_rank]), the other to the pages
+ * [pages, 64, kv_rank] at each row's position.  The attention over the latent itself is pieh_bias_attn_run with one
+ * key / value head of kv_rank features whose key and value pages are the same pool. */
+int pieh_latent_prepare(void* cq_out, int out_dtype, const float* proj, long long ld, int q_rank, long long kv_off,
+                        int kv_rank, const float* q_norm, const float* kv_norm, float eps, void* pages, int kv_dtype,
+                        const pieh_batch* b, void* stream);
 
 #ifdef __cplusplus
 }

@@ -165,7 +165,10 @@ class HybBiasAttn(C.Structure):
                 ("v_off", C.c_longlong), ("g_off", C.c_longlong), ("q_norm", C.c_void_p), ("k_norm", C.c_void_p),
                 ("eps", C.c_float), ("scale", C.c_float), ("temp_coef", C.c_float), ("temp_every", C.c_double),
                 ("slopes", C.c_void_p), ("sink", C.c_int), ("window", C.c_int), ("k_pages", C.c_void_p),
-                ("v_pages", C.c_void_p), ("kv_dtype", C.c_int)]
+                ("v_pages", C.c_void_p), ("kv_dtype", C.c_int),
+                # optional pieces, zero / NULL = off
+                ("sinks", C.c_void_p), ("gate_heads", C.c_int), ("rot_dims", C.c_int), ("rot_cs", C.c_void_p),
+                ("v_mix", C.c_void_p), ("v_keep", C.c_void_p)]
 
 
 class HybMixSum(C.Structure):
@@ -178,11 +181,18 @@ class HybMoePlan(C.Structure):
     """pieh_moe_plan"""
     _fields_ = [("E", C.c_int), ("top", C.c_int), ("n_groups", C.c_int), ("keep_groups", C.c_int), ("scale", C.c_float),
                 ("slot_row", C.c_void_p), ("slot_expert", C.c_void_p), ("pair_slot", C.c_void_p), ("pair_w", C.c_void_p),
-                ("tiles64", C.c_void_p), ("tiles128", C.c_void_p), ("counters", C.c_void_p)]
+                ("tiles64", C.c_void_p), ("tiles128", C.c_void_p), ("counters", C.c_void_p), ("softmax_top", C.c_int)]
+
+
+class HybCanon(C.Structure):
+    """pieh_canon"""
+    _fields_ = [("taps", C.c_int), ("n_out", C.c_int), ("w", C.c_void_p * 4), ("out", C.c_void_p * 4),
+                ("state", C.c_void_p)]
 
 
 _PB, _PD, _PA = C.POINTER(HybBatch), C.POINTER(HybDelta), C.POINTER(HybAttn)
 _PBA, _PMS, _PMP = C.POINTER(HybBiasAttn), C.POINTER(HybMixSum), C.POINTER(HybMoePlan)
+_PCN = C.POINTER(HybCanon)
 # libpie_b200_hybrid.so: every symbol include/pie_b200_hybrid.h declares (tests check this), + the page allocator
 HYBRID_SIGNATURES = {
     "pieh_abi_version": (_i, []),
@@ -204,11 +214,18 @@ HYBRID_SIGNATURES = {
     "pieh_postnorm_add": (_i, [_vp, _vp, _i, _vp, _PMS, _vp, _f, _i, _i, _vp]),
     "pieh_bias_attn_prepare": (_i, [_vp, _vp, _ll, _PBA, _PB, _vp]),
     "pieh_bias_attn_run": (_i, [_vp, _i, _vp, _vp, _ll, _PBA, _PB, _vp]),
+    "pieh_linear_batched": (_i, [_vp, _i, _ll, _ll, _vp, _i, _ll, _ll, _vp, _i, _ll, _i, _i, _i, _i, _i, _vp, _ll, _ll, _vp]),
+    "pieh_rot_table": (_i, [_vp, _vp, _vp, _i, _i, _vp]),
+    "pieh_embed_scaled": (_i, [_vp, _vp, _i, _vp, _f, _i, _i, _i, _vp]),
+    "pieh_residual_norm": (_i, [_vp, _vp, _PMS, _vp, _vp, _f, _i, _i, _vp]),
+    "pieh_canon_conv": (_i, [_PCN, _i, _vp, _i, _PB, _vp]),
+    "pieh_mingru_scan": (_i, [_vp, _i, _vp, _ll, _i, _vp, _PB, _vp]),
+    "pieh_latent_prepare": (_i, [_vp, _i, _vp, _ll, _i, _ll, _i, _vp, _vp, _f, _vp, _i, _PB, _vp]),
     "pieh_moe_route": (_i, [_vp, _ll, _PMP, _i, _vp]),
     "pieh_moe_linear": (_i, [_vp, _i, _ll, _vp, _i, _ll, _vp, _i, _ll, _i, _i, _i, _i, _i, _f, _f, _f, _PMP, _vp]),
 }
 HYBRID_LIB_PATH = os.environ.get("PIE_HYBRID_LIB") or os.path.join(_HERE, "libpie_b200_hybrid.so")
-EPI_NONE, EPI_RELU2, EPI_SOFTCAP, EPI_STREAMS = 0, 1, 2, 3
+EPI_NONE, EPI_RELU2, EPI_SOFTCAP, EPI_STREAMS, EPI_GLU, EPI_SIGMUL = 0, 1, 2, 3, 4, 5
 
 _lib = None
 _hyb = None

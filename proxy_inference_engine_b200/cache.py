@@ -204,7 +204,9 @@ class HybridCache:
     * attention layers: key / value page pools ``[pages, 64, G, key_width]`` / ``[pages, 64, G, dv]`` in the act dtype
       (key_width: 2 d for the two maps of differential attention unless the layer's spec names another), indexed
       by the page ids of ONE ``paging.PageAllocator`` (a page id names the same 64 positions in every layer's pools);
-    * recurrent layers: per state slot the matrix state ``[H, dk, dv]`` and the convolution history ``[taps - 1, C]``, fp32.
+    * recurrent layers: per state slot the matrix state ``[H, dk, dv]`` and the convolution history ``[taps - 1, C]``, fp32;
+    * a spec of the form ``{"pages": {name: shape}, "slots": {name: shape}}`` names its pools and slot tensors itself (a
+      layer may hold both: attention pages beside a convolution history).
 
     ``admit`` gives a sequence a slot, ``reserve`` grows its page list to cover a length, ``release`` hands both back
     (LIFO, so the next sequence re-uses them).  Nothing is cleared on re-use: a recurrent operator starts a sequence with
@@ -221,8 +223,19 @@ class HybridCache:
         self.free_slots = list(range(self.max_seqs - 1, -1, -1))
         self.seqs = {}     # id -> {"slot", "pages", "length"}
         self.layers = []
+        self.slot_keys = {"state", "conv"}     # entries that live in state slots (what a replayed step must put back)
         for spec in layer_specs:
-            if spec["kind"] == "attention":
+            if "pages" in spec or "slots" in spec:
+                # the general form: named page pools [pages, 64, *shape] in the act dtype and named per-slot tensors
+                # [slots, *shape] in fp32, whatever mixture of the two a layer needs
+                entry = {}
+                for name, shape in (spec.get("pages") or {}).items():
+                    entry[name] = torch.zeros((self.n_pages, self.page_size, *shape), dtype=act_dtype, device=device)
+                for name, shape in (spec.get("slots") or {}).items():
+                    entry[name] = torch.zeros((self.max_seqs, *shape), dtype=torch.float32, device=device)
+                    self.slot_keys.add(name)
+                self.layers.append(entry)
+            elif spec["kind"] == "attention":
                 G, d2, dv = spec["G"], int(spec.get("key_width") or 2 * spec["d"]), spec["dv"]
                 self.layers.append({"k": torch.zeros((self.n_pages, self.page_size, G, d2), dtype=act_dtype, device=device),
                                     "v": torch.zeros((self.n_pages, self.page_size, G, dv), dtype=act_dtype, device=device)})

@@ -247,9 +247,14 @@ def _load_babodra(config: dict, path: str, device, dtype):
     return BabodraModel(BabodraArgs.from_dict(config), read_weights(path), device, dtype or "bfloat16")
 
 
+def _load_maginex(config: dict, path: str, device, dtype):
+    from .maginex import MaginexArgs, MaginexModel
+    return MaginexModel(MaginexArgs.from_dict(config), read_weights(path), device, dtype or "bfloat16")
+
+
 # model registry: config.json's "architecture" (or, for Hugging Face / MLX checkpoints, "model_type") -> loader.
 # The reference resolves model_type to a module of PIE/models/ the same way (PIE/models/utils.py:25-48).
-MODEL_REGISTRY = {"llama": _load_llama, "Golitar": _load_golitar, "Babodra": _load_babodra}
+MODEL_REGISTRY = {"llama": _load_llama, "Golitar": _load_golitar, "Babodra": _load_babodra, "Maginex": _load_maginex}
 
 
 def model_kind(config: dict) -> str:

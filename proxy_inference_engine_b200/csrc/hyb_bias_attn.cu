@@ -3,6 +3,9 @@
 //   p_ij = exp(s_ij) / (sink + sum_j exp(s_ij))          sink = 1: a term of score 0 that carries no value, so a query
 //                                                        that matches nothing returns (almost) nothing
 //   out_i = sum_j p_ij v_j * sigmoid(gate_i)
+// Optional: a LEARNED sink logit per head in place of the score-0 sink, one gate logit per head in place of one per
+// feature, a rotation of the leading features of every query / key head ("rotate half" pairing) from a per-step (cos, sin)
+// table, and values blended with another layer's values of the same token before they are cached.
 // bias_prepare_kernel   per token: ONE rms norm over all heads' query features (and one over all key features) with
 //                       per-feature weights, the query temperature 1 + c ln(floor((p + 1) / every) + 1), then the normed
 //                       keys go to the key pages and the values -- here usually the PROJECTED keys themselves, v_off ==
@@ -48,10 +51,29 @@ __global__ void __launch_bounds__(256) bias_prepare_kernel(float* q_out, const f
   const size_t slot = (size_t)b.block_table[(size_t)i * b.bt_stride + p / kPage] * kPage + p % kPage;
   KT* kp = reinterpret_cast<KT*>(a.k_pages) + slot * nk;
   KT* vp = reinterpret_cast<KT*>(a.v_pages) + slot * nv;
-  for (int c = threadIdx.x; c < nq; c += blockDim.x) q_out[(size_t)t * nq + c] = row[c] * iq * (a.q_norm ? a.q_norm[c] : 1.f);
-  for (int c = threadIdx.x; c < nk; c += blockDim.x)
-    elem<KT>::store(kp + c, row[a.k_off + c] * ik * (a.k_norm ? a.k_norm[c] : 1.f));
-  for (int c = threadIdx.x; c < nv; c += blockDim.x) elem<KT>::store(vp + c, row[a.v_off + c]);
+  // feature c of a projection after its norm and, for the leading rot_dims features of a head, the rotation that pairs
+  // feature f with f + rot_dims / 2
+  const int half = a.rot_dims >> 1;
+  const float* cs = a.rot_cs ? a.rot_cs + (size_t)t * half * 2 : nullptr;
+  auto feat = [&](const float* x, const float* nw, float inv, int c) {
+    const float v = x[c] * inv * (nw ? nw[c] : 1.f);
+    const int f = c % a.d;
+    if (!cs || f >= a.rot_dims) return v;
+    const bool lo = f < half;
+    const int o = lo ? c + half : c - half;
+    const float u = x[o] * inv * (nw ? nw[o] : 1.f);
+    const float co = cs[2 * (lo ? f : f - half)], si = cs[2 * (lo ? f : f - half) + 1];
+    return lo ? v * co - u * si : v * co + u * si;
+  };
+  for (int c = threadIdx.x; c < nq; c += blockDim.x) q_out[(size_t)t * nq + c] = feat(row, a.q_norm, iq, c);
+  for (int c = threadIdx.x; c < nk; c += blockDim.x) elem<KT>::store(kp + c, feat(row + a.k_off, a.k_norm, ik, c));
+  const float lam = a.v_mix ? *a.v_mix : 0.f;
+  for (int c = threadIdx.x; c < nv; c += blockDim.x) {
+    float v = row[a.v_off + c];
+    if (a.v_mix) v = (1.f - lam) * v + lam * a.v_keep[(size_t)t * nv + c];
+    else if (a.v_keep) a.v_keep[(size_t)t * nv + c] = v;
+    elem<KT>::store(vp + c, v);
+  }
 }
 
 constexpr int kRunWarps = 8;
@@ -159,43 +181,60 @@ __global__ void __launch_bounds__(kRunWarps * 32) bias_run_kernel(OT* out, const
   }
   if (lane == 0) { mine[dv] = m; mine[dv + 1] = l; }
   __syncthreads();
-  const int c = threadIdx.x;   // dv <= 256 = threads
-  if (c < dv) {                // the warps of this CTA -> one partial softmax
-    float M = -1e30f;
+  {                            // the warps of this CTA -> one partial softmax
+    float M = -1e30f, f[NW], L = 0.f;
+#pragma unroll
     for (int w = 0; w < NW; ++w) M = fmaxf(M, mg[(size_t)w * (dv + 2) + dv]);
-    float L = 0.f, A = 0.f;
+#pragma unroll
     for (int w = 0; w < NW; ++w) {
-      const float* src = mg + (size_t)w * (dv + 2);
-      const float f = expf(src[dv] - M);
-      L = fmaf(src[dv + 1], f, L);
-      A = fmaf(src[c], f, A);
+      f[w] = expf(mg[(size_t)w * (dv + 2) + dv] - M);
+      L = fmaf(mg[(size_t)w * (dv + 2) + dv + 1], f[w], L);
     }
-    part[c] = A;
-    if (c == 0) { part[dv] = M; part[dv + 1] = L; }
+    for (int c = threadIdx.x; c < dv; c += NTH) {
+      float A = 0.f;
+#pragma unroll
+      for (int w = 0; w < NW; ++w) A = fmaf(mg[(size_t)w * (dv + 2) + c], f[w], A);
+      part[c] = A;
+    }
+    if (threadIdx.x == 0) { part[dv] = M; part[dv + 1] = L; }
   }
   if (CLUSTER) cg::this_cluster().sync(); else __syncthreads();
-  if (rank == 0 && c < dv) {   // the CTAs of the cluster and the sink -> the output
-    float M = a.sink ? 0.f : -1e30f;   // the sink is one more partial softmax: maximum 0, sum 1, no values
-    float L = 0.f, A = 0.f;
+  if (rank == 0) {   // the CTAs of the cluster and the sink -> the output
+    // the sink is one more partial softmax: maximum = its logit (0 for the fixed sink), sum 1, no values
+    const bool has_sink = a.sinks != nullptr || a.sink != 0;
+    const float sk = a.sinks ? a.sinks[h] : 0.f;
+    float M = has_sink ? sk : -1e30f;
+    float L = 0.f;
+    const float* gate = a.g_off >= 0 ? proj + (size_t)t * ld + a.g_off + (a.gate_heads ? (size_t)h : (size_t)h * dv) : nullptr;
     if (CLUSTER) {
       cg::cluster_group cl = cg::this_cluster();
       for (int r = 0; r < cs; ++r) M = fmaxf(M, cl.map_shared_rank(part, r)[dv]);
       for (int r = 0; r < cs; ++r) {
         const float* src = cl.map_shared_rank(part, r);
-        const float f = expf(src[dv] - M);
-        L = fmaf(src[dv + 1], f, L);
-        A = fmaf(src[c], f, A);
+        L = fmaf(src[dv + 1], expf(src[dv] - M), L);
+      }
+      if (has_sink) L += expf(sk - M);
+      for (int c = threadIdx.x; c < dv; c += NTH) {
+        float A = 0.f;
+        for (int r = 0; r < cs; ++r) {
+          const float* src = cl.map_shared_rank(part, r);
+          A = fmaf(src[c], expf(src[dv] - M), A);
+        }
+        float o = A / L;
+        if (gate) o *= 1.f / (1.f + expf(-gate[a.gate_heads ? 0 : c]));
+        elem<OT>::store(out + ((size_t)t * a.H + h) * dv + c, o);
       }
     } else {
       M = fmaxf(M, part[dv]);
       const float f = expf(part[dv] - M);
       L = part[dv + 1] * f;
-      A = part[c] * f;
+      if (has_sink) L += expf(sk - M);
+      for (int c = threadIdx.x; c < dv; c += NTH) {
+        float o = part[c] * f / L;
+        if (gate) o *= 1.f / (1.f + expf(-gate[a.gate_heads ? 0 : c]));
+        elem<OT>::store(out + ((size_t)t * a.H + h) * dv + c, o);
+      }
     }
-    if (a.sink) L += expf(-M);
-    float o = A / L;
-    if (a.g_off >= 0) o *= 1.f / (1.f + expf(-proj[(size_t)t * ld + a.g_off + (size_t)h * dv + c]));
-    elem<OT>::store(out + ((size_t)t * a.H + h) * dv + c, o);
   }
   if (CLUSTER) cg::this_cluster().sync();   // nobody's shared memory goes away while the first CTA still reads it
 }
@@ -286,12 +325,14 @@ __global__ void __launch_bounds__(128) bias_tile_kernel(__nv_bfloat16* out, cons
   float o[DT][4];
 #pragma unroll
   for (int x = 0; x < DT; ++x) o[x][0] = o[x][1] = o[x][2] = o[x][3] = 0.f;
-  const float m_init = a.sink ? 0.f : -INFINITY;
+  constexpr float kLog2e = 1.4426950408889634f;
+  const bool has_sink = a.sinks != nullptr || a.sink != 0;
+  const float sk2 = a.sinks ? a.sinks[h] * kLog2e : 0.f;   // the sink's logit in the exp2 domain
+  const float m_init = has_sink ? sk2 : -INFINITY;
   float mrun[2] = {m_init, m_init}, lrun[2] = {0.f, 0.f};
   const int p0 = pos0 + min(r0, nrows - 1), p1 = pos0 + min(r1, nrows - 1);   // positions of this thread's two rows
   const int w0 = a.window > 0 ? p0 - a.window + 1 : 0, w1 = a.window > 0 ? p1 - a.window + 1 : 0;
   const float slope = a.slopes ? a.slopes[h] : 0.f;
-  constexpr float kLog2e = 1.4426950408889634f;
 
   for (int j = j_lo; j <= j_hi; ++j) {
     if (j < j_hi) { issue(j + 1); asm volatile("cp.async.wait_group 1;" ::: "memory"); }
@@ -371,18 +412,20 @@ __global__ void __launch_bounds__(128) bias_tile_kernel(__nv_bfloat16* out, cons
   for (int rr = 0; rr < 2; ++rr) {
     float l = lrun[rr];
     l += __shfl_xor_sync(0xffffffffu, l, 1); l += __shfl_xor_sync(0xffffffffu, l, 2);
-    if (a.sink) l += exp2f(-mrun[rr]);   // the sink's score 0 against the running maximum
+    if (has_sink) l += exp2f(sk2 - mrun[rr]);   // the sink's logit against the running maximum
     inv[rr] = 1.f / l;
   }
-  const float* g0 = a.g_off >= 0 ? proj + (size_t)(row0 + min(r0, nrows - 1)) * ld + a.g_off + (size_t)h * DV : nullptr;
-  const float* g1 = a.g_off >= 0 ? proj + (size_t)(row0 + min(r1, nrows - 1)) * ld + a.g_off + (size_t)h * DV : nullptr;
+  const size_t goff = a.g_off + (a.gate_heads ? (size_t)h : (size_t)h * DV);
+  const float* g0 = a.g_off >= 0 ? proj + (size_t)(row0 + min(r0, nrows - 1)) * ld + goff : nullptr;
+  const float* g1 = a.g_off >= 0 ? proj + (size_t)(row0 + min(r1, nrows - 1)) * ld + goff : nullptr;
+  const int gs = a.gate_heads ? 0 : 1;   // one logit per head, or one per output feature
 #pragma unroll
   for (int x = 0; x < DT; ++x) {
     const int c = x * 8 + 2 * t4;
     float y0 = o[x][0] * inv[0], y1 = o[x][1] * inv[0], y2 = o[x][2] * inv[1], y3 = o[x][3] * inv[1];
     if (g0) {
-      y0 *= 1.f / (1.f + __expf(-g0[c])); y1 *= 1.f / (1.f + __expf(-g0[c + 1]));
-      y2 *= 1.f / (1.f + __expf(-g1[c])); y3 *= 1.f / (1.f + __expf(-g1[c + 1]));
+      y0 *= 1.f / (1.f + __expf(-g0[gs * c])); y1 *= 1.f / (1.f + __expf(-g0[gs * (c + 1)]));
+      y2 *= 1.f / (1.f + __expf(-g1[gs * c])); y3 *= 1.f / (1.f + __expf(-g1[gs * (c + 1)]));
     }
     if (r0 < nrows) *reinterpret_cast<uint32_t*>(out + ((size_t)(row0 + r0) * a.H + h) * DV + c) = pack2(y0, y1);
     if (r1 < nrows) *reinterpret_cast<uint32_t*>(out + ((size_t)(row0 + r1) * a.H + h) * DV + c) = pack2(y2, y3);
@@ -412,8 +455,10 @@ static bool tile_ok(const pieh_bias_attn& a, const pieh_batch& b, int out_dtype)
 }
 
 static bool bias_attn_ok(const pieh_bias_attn* a) {
-  return a && a->H > 0 && a->G > 0 && a->H % a->G == 0 && a->d > 0 && a->dv > 0 && a->dv <= 256 && a->d <= 1024 &&
-         a->k_pages && a->v_pages && a->temp_every >= 0.0 && a->window >= 0 && a->k_off >= 0 && a->v_off >= 0;
+  return a && a->H > 0 && a->G > 0 && a->H % a->G == 0 && a->d > 0 && a->dv > 0 && a->dv <= 512 && a->d <= 1024 &&
+         a->k_pages && a->v_pages && a->temp_every >= 0.0 && a->window >= 0 && a->k_off >= 0 && a->v_off >= 0 &&
+         a->rot_dims >= 0 && a->rot_dims <= a->d && (a->rot_dims & 1) == 0 && (a->rot_dims == 0 || a->rot_cs) &&
+         (!a->v_mix || a->v_keep);
 }
 
 template <typename KT, typename OT, int NV>
@@ -449,7 +494,8 @@ static cudaError_t launch_run(OT* out, const float* q, const float* proj, long l
   if (nv <= 1) return launch_run_nv<KT, OT, 1>(out, q, proj, ld, a, b, st);
   if (nv <= 2) return launch_run_nv<KT, OT, 2>(out, q, proj, ld, a, b, st);
   if (nv <= 4) return launch_run_nv<KT, OT, 4>(out, q, proj, ld, a, b, st);
-  return launch_run_nv<KT, OT, 8>(out, q, proj, ld, a, b, st);
+  if (nv <= 8) return launch_run_nv<KT, OT, 8>(out, q, proj, ld, a, b, st);
+  return launch_run_nv<KT, OT, 16>(out, q, proj, ld, a, b, st);
 }
 
 }  // namespace pieh

@@ -53,6 +53,11 @@ struct LinArgs {
   const int32_t* g_rows = nullptr;          // x row of each slot (NULL: the slot itself)
   const int32_t* g_expert = nullptr;        // expert of each slot (the decode kernel: one slot per blockIdx.y)
   long long g_wstride = 0;                  // elements between two experts' matrices
+  // batched mode (pieh_linear_batched): blockIdx.z picks one of nb independent products
+  long long x_bs = 0, w_bs = 0, out_bs = 0; // elements between two products' operands
+  const float* gate = nullptr;              // SIGMUL: fp32 logits, element z * gate_bs + m * gate_ld + n
+  long long gate_ld = 0, gate_bs = 0;
+  int nb = 1;
 };
 
 // the gated pair of PIEH_EPI_GLU: g the gate column, u the linear one

@@ -21,6 +21,7 @@ __device__ __forceinline__ void lin_store(const LinArgs& a, int m, int n, float 
   if (a.bias) y += a.bias[n];
   if (a.epi == PIEH_EPI_RELU2) { y = fmaxf(y, 0.f); y = y * y; }
   else if (a.epi == PIEH_EPI_SOFTCAP) y = a.epi_a * tanhf(y / a.epi_a);
+  else if (a.epi == PIEH_EPI_SIGMUL) y *= 1.f / (1.f + expf(-a.gate[(size_t)blockIdx.z * a.gate_bs + (size_t)m * a.gate_ld + n]));
   if (a.epi == PIEH_EPI_STREAMS) {
     float* xs = reinterpret_cast<float*>(a.out) + (size_t)m * a.S * a.N + n;
     float old[8];
@@ -32,7 +33,7 @@ __device__ __forceinline__ void lin_store(const LinArgs& a, int m, int n, float 
     }
     return;
   }
-  elem<OT>::store(reinterpret_cast<OT*>(a.out) + (size_t)m * a.out_ld + n, y);
+  elem<OT>::store(reinterpret_cast<OT*>(a.out) + (size_t)blockIdx.z * a.out_bs + (size_t)m * a.out_ld + n, y);
 }
 
 template <typename OT>
@@ -49,8 +50,8 @@ __global__ void __launch_bounds__(256) linear_tile_kernel(const LinArgs a) {
   const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
   int m0 = blockIdx.y * BM, m_end = a.M;
   const int n0 = blockIdx.x * BN;
-  const XT* x = reinterpret_cast<const XT*>(a.x);
-  const WT* w = reinterpret_cast<const WT*>(a.w);
+  const XT* x = reinterpret_cast<const XT*>(a.x) + (size_t)blockIdx.z * a.x_bs;
+  const WT* w = reinterpret_cast<const WT*>(a.w) + (size_t)blockIdx.z * a.w_bs;
   if (a.g_tiles) {   // grouped: this CTA's rows are one expert's run of slots
     if ((int)blockIdx.y >= a.g_tiles[0]) return;
     const int32_t* tl = a.g_tiles + 1 + 3 * blockIdx.y;
@@ -133,8 +134,8 @@ __global__ void __launch_bounds__(256) linear_rows_kernel(const LinArgs a) {
   pdl_sync();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n0 = blockIdx.x * R;
-  const XT* x = reinterpret_cast<const XT*>(a.x);
-  const WT* w = reinterpret_cast<const WT*>(a.w);
+  const XT* x = reinterpret_cast<const XT*>(a.x) + (size_t)blockIdx.z * a.x_bs;
+  const WT* w = reinterpret_cast<const WT*>(a.w) + (size_t)blockIdx.z * a.w_bs;
   int mb = 0, M = a.M;   // grouped: one slot per blockIdx.y, with its own expert's matrix
   if (a.g_expert) {
     mb = blockIdx.y;
@@ -238,10 +239,11 @@ __global__ void __launch_bounds__(256) linear_skinny_kernel(const LinArgs a) {
 template <typename XT, typename WT, typename OT>
 static cudaError_t launch_typed(const LinArgs& a, cudaStream_t st) {
   const bool vec_ok = a.K % 8 == 0 && a.x_ld % 8 == 0 && (reinterpret_cast<uintptr_t>(a.x) & 31) == 0 &&
-                      (reinterpret_cast<uintptr_t>(a.w) & 31) == 0;
+                      (reinterpret_cast<uintptr_t>(a.w) & 31) == 0 && a.x_bs % 8 == 0 && a.w_bs % 8 == 0;
+  const unsigned nb = (unsigned)a.nb;
   count_launch();
   cudaError_t e = cudaSuccess;
-  if (!a.g_tiles && a.M > 32 && a.N <= 32 && vec_ok && a.epi != PIEH_EPI_GLU) {
+  if (!a.g_tiles && a.nb == 1 && a.M > 32 && a.N <= 32 && vec_ok && a.epi != PIEH_EPI_GLU) {
     const dim3 grid((a.M + 7) / 8);
     if (a.N <= 8) e = launch_k(linear_skinny_kernel<XT, WT, OT, 8>, grid, dim3(256), 0, st, a);
     else if (a.N <= 16) e = launch_k(linear_skinny_kernel<XT, WT, OT, 16>, grid, dim3(256), 0, st, a);
@@ -260,8 +262,8 @@ static cudaError_t launch_typed(const LinArgs& a, cudaStream_t st) {
     }
   } else if (a.M <= 32 && vec_ok) {
     // rows per CTA: enough to amortise the activation loads, few enough that every SM still gets several CTAs
-    const bool wide = a.N >= 4 * 4 * num_sms() || a.epi == PIEH_EPI_GLU;   // a gated pair needs an even row count
-#define PIEH_ROWS(MR, R) e = launch_k(linear_rows_kernel<XT, WT, OT, MR, R>, dim3((a.N + R - 1) / R), dim3(256), 0, st, a)
+    const bool wide = (long long)a.N * a.nb >= 4 * 4 * num_sms() || a.epi == PIEH_EPI_GLU;   // a gated pair needs an even row count
+#define PIEH_ROWS(MR, R) e = launch_k(linear_rows_kernel<XT, WT, OT, MR, R>, dim3((a.N + R - 1) / R, 1, nb), dim3(256), 0, st, a)
     if (a.M <= 1) { if (wide) PIEH_ROWS(1, 2); else PIEH_ROWS(1, 1); }
     else if (a.M <= 4) { if (wide) PIEH_ROWS(4, 4); else PIEH_ROWS(4, 2); }
     else if (a.M <= 8) { if (wide) PIEH_ROWS(8, 4); else PIEH_ROWS(8, 2); }
@@ -269,7 +271,7 @@ static cudaError_t launch_typed(const LinArgs& a, cudaStream_t st) {
     else PIEH_ROWS(32, 2);
 #undef PIEH_ROWS
   } else {
-    const dim3 grid((a.N + 63) / 64, (a.M + 63) / 64);
+    const dim3 grid((a.N + 63) / 64, (a.M + 63) / 64, nb);
     e = launch_k(linear_tile_kernel<XT, WT, OT>, grid, dim3(256), 0, st, a);
   }
   return e;
@@ -333,10 +335,10 @@ extern "C" int pieh_moe_linear(void* out, int out_dtype, long long out_ld, const
                                const void* w, int w_dtype, long long w_stride, int P, int N, int K, int gather_rows, int glu,
                                float alpha, float limit, float up_offset, const pieh_moe_plan* p, void* stream) {
   if (!out || !x || !w || !p || !p->tiles64 || !p->tiles128 || !p->slot_row || !p->slot_expert) return PIE_ENULL;
-  if (P < 0 || N <= 0 || K <= 0 || (glu && (N & 1)) || p->E < 1 || limit < 0.f) return PIE_EINVAL_SHAPE;
+  if (P < 0 || N <= 0 || K <= 0 || glu < 0 || glu > 2 || (glu == 1 && (N & 1)) || p->E < 1 || limit < 0.f) return PIE_EINVAL_SHAPE;
   if (P == 0) return PIE_OK;
-  LinArgs a{out, out_ld, x, x_ld, w, nullptr, P, N, K, glu ? PIEH_EPI_GLU : PIEH_EPI_NONE, glu ? limit : 0.f, nullptr, nullptr,
-            p->E};
+  LinArgs a{out, out_ld, x, x_ld, w, nullptr, P, N, K, glu == 1 ? PIEH_EPI_GLU : glu == 2 ? PIEH_EPI_RELU2 : PIEH_EPI_NONE,
+            glu == 1 ? limit : 0.f, nullptr, nullptr, p->E};
   a.epi_b = alpha;
   a.epi_c = up_offset;
   a.g_tiles = p->tiles64;
@@ -344,5 +346,21 @@ extern "C" int pieh_moe_linear(void* out, int out_dtype, long long out_ld, const
   a.g_rows = gather_rows ? p->slot_row : nullptr;
   a.g_expert = p->slot_expert;
   a.g_wstride = w_stride;
+  return run_linear(a, out_dtype, x_dtype, w_dtype, (cudaStream_t)stream);
+}
+
+extern "C" int pieh_linear_batched(void* out, int out_dtype, long long out_ld, long long out_bs, const void* x, int x_dtype,
+                                   long long x_ld, long long x_bs, const void* w, int w_dtype, long long w_bs, int nb, int M,
+                                   int N, int K, int epilogue, const float* gate, long long gate_ld, long long gate_bs,
+                                   void* stream) {
+  if (!out || !x || !w) return PIE_ENULL;
+  if (M < 0 || N <= 0 || K <= 0 || nb < 1 || nb > 65535) return PIE_EINVAL_SHAPE;
+  if (M == 0) return PIE_OK;
+  if (epilogue != PIEH_EPI_NONE && epilogue != PIEH_EPI_RELU2 && epilogue != PIEH_EPI_SIGMUL) return PIE_EUNSUPPORTED;
+  if (epilogue == PIEH_EPI_SIGMUL && !gate) return PIE_ENULL;
+  LinArgs a{out, out_ld, x, x_ld, w, nullptr, M, N, K, epilogue, 0.f, nullptr, nullptr, 0};
+  a.x_bs = x_bs; a.w_bs = w_bs; a.out_bs = out_bs;
+  a.gate = gate; a.gate_ld = gate_ld; a.gate_bs = gate_bs;
+  a.nb = nb;
   return run_linear(a, out_dtype, x_dtype, w_dtype, (cudaStream_t)stream);
 }

@@ -1,5 +1,6 @@
 // Mixture-of-experts routing and the plan of the grouped products.
-//   moe_route_kernel   one warp per token: sigmoid scores, group scores (sum of a group's two largest), the best groups
+//   moe_route_kernel   one warp per token.  softmax_top: the largest logits, weights = softmax over the chosen logits.
+//                      Otherwise: sigmoid scores, group scores (sum of a group's two largest), the best groups
 //                      stay eligible, the `top` largest eligible scores are chosen (ties: lower index) with weight
 //                      score * scale; it also counts the tokens of every expert
 //   moe_plan_kernel    one CTA: prefix sums of the counts -> every (token, choice) pair gets a SLOT in its expert's run,
@@ -20,6 +21,39 @@ __global__ void __launch_bounds__(32) moe_route_kernel(const float* z, long long
   pdl_sync();
   const int t = blockIdx.x, lane = threadIdx.x;
   const int E = p.E, per = E / p.n_groups;
+  if (p.softmax_top) {
+    // the `top` largest logits, weighted by the softmax over those logits alone (ties: lower index)
+    __shared__ float chosen[kMaxTop];
+    for (int e = lane; e < E; e += 32) s[e] = z[(size_t)t * ld + e];
+    __syncwarp();
+    for (int r = 0; r < p.top; ++r) {
+      float bv = -INFINITY;
+      int bi = E;
+      for (int i = lane; i < E; i += 32)
+        if (s[i] > bv) { bv = s[i]; bi = i; }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+      }
+      __syncwarp();
+      if (lane == 0) {
+        const int ee = bi < E ? bi : 0;
+        chosen[r] = bi < E ? bv : -INFINITY;
+        p.pair_slot[(size_t)t * p.top + r] = ee;
+        atomicAdd(&p.counters[ee], 1);
+        if (bi < E) s[ee] = -INFINITY;   // taken
+      }
+      __syncwarp();
+    }
+    if (lane == 0) {
+      float sum = 0.f;
+      for (int r = 0; r < p.top; ++r) sum += expf(chosen[r] - chosen[0]);   // chosen[0] is the largest
+      for (int r = 0; r < p.top; ++r) p.pair_w[(size_t)t * p.top + r] = expf(chosen[r] - chosen[0]) / sum * p.scale;
+    }
+    return;
+  }
   for (int e = lane; e < E; e += 32) s[e] = 1.f / (1.f + expf(-z[(size_t)t * ld + e]));
   __syncwarp();
   for (int g = lane; g < p.n_groups; g += 32) {

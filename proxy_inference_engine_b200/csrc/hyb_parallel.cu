@@ -1,0 +1,266 @@
+// Pieces of parallel pre-norm blocks (one norm feeds the mixer and the feed-forward, both outputs join the residual together):
+//   embed_scaled_kernel    x[t] = table[token] * scale
+//   residual_norm_kernel   x[t] += y[t] + mixture of experts' rows (+ shared rows);  h[t] = rms_norm(x[t]) * w  -- the next
+//                          block's norm in the pass that closes this block, so the residual is read once per block
+//   canon_kernel           out_k[t] = h[t] + causal per-channel convolution of h (several tap sets over one h); rows before
+//                          the step come from the sequence's state slot, rows before the sequence are zero
+//   canon_state_kernel     afterwards: the last taps - 1 rows of h of every sequence become its state
+//   mingru_scan_kernel     S_t = (1 - z_t) S_(t-1) + z_t c_t per channel, a thread per channel walking the sequence's rows
+//                          in runs of 8 whose loads and gate arithmetic do not wait for the recurrence
+//   latent_prepare_kernel  the two RMS norms of latent attention: query latent -> act tensor, key / value latent -> pages
+//   rot_table_kernel       (cos, sin) of every row's rotation angles, formed once per step for all layers that share them
+#include "hyb_common.cuh"
+
+namespace pieh {
+
+constexpr int kPageTokens = 64;
+
+template <typename ET>
+__global__ void embed_scaled_kernel(float* x, const ET* table, const int32_t* tokens, float scale, int W, int vocab) {
+  pdl_sync();
+  const int t = blockIdx.x;
+  int id = tokens[t];
+  id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);
+  const ET* row = table + (size_t)id * W;
+  for (int c = threadIdx.x; c < W; c += blockDim.x) x[(size_t)t * W + c] = elem<ET>::load(row + c) * scale;
+}
+
+__global__ void __launch_bounds__(256) residual_norm_kernel(float* x, const float* y, const pieh_mix_sum mix, float* h,
+                                                            const float* norm_w, float eps, int W) {
+  extern __shared__ float row[];
+  __shared__ float red[33];
+  pdl_sync();
+  const int t = blockIdx.x;
+  float ss = 0.f;
+  float sg = 1.f;
+  if (mix.parts && mix.shared && mix.shared_gate) sg = 1.f / (1.f + expf(-mix.shared_gate[(size_t)t * mix.gate_ld]));
+  for (int c = threadIdx.x; c < W; c += blockDim.x) {
+    float add = y ? y[(size_t)t * W + c] : 0.f;
+    if (mix.parts) {
+      float v = 0.f;
+      for (int k = 0; k < mix.top; ++k)   // choice order: the sum does not depend on how the slots were handed out
+        v = fmaf(mix.part_w[(size_t)t * mix.top + k], mix.parts[(size_t)mix.part_row[(size_t)t * mix.top + k] * W + c], v);
+      if (mix.shared) v = fmaf(sg, mix.shared[(size_t)t * W + c], v);
+      add += v;
+    }
+    float v = x[(size_t)t * W + c];
+    if (y || mix.parts) {
+      v += add;
+      x[(size_t)t * W + c] = v;
+    }
+    row[c] = v;
+    ss = fmaf(v, v, ss);
+  }
+  if (!h || !norm_w) return;
+  ss = block_sum(ss, red);
+  const float inv = 1.f / sqrtf(ss / (float)W + eps);
+  for (int c = threadIdx.x; c < W; c += blockDim.x) h[(size_t)t * W + c] = row[c] * inv * norm_w[c];
+}
+
+constexpr int kMaxTaps = 8;
+
+template <typename OT>
+__global__ void __launch_bounds__(256) canon_kernel(const pieh_canon cn, const float* h, int W, const pieh_batch b) {
+  pdl_sync();
+  const int t = blockIdx.x;
+  const int i = b.tok_seq[t], p = b.tok_pos[t], ctx = b.seq_ctx[i];
+  const int taps = cn.taps;
+  const float* hist = cn.state + (size_t)b.seq_slot[i] * (taps - 1) * W;
+  for (int c = threadIdx.x; c < W; c += blockDim.x) {
+    float past[kMaxTaps];   // past[j]: h of position p - taps + 1 + j; past[taps - 1] is this row
+#pragma unroll
+    for (int j = 0; j < kMaxTaps; ++j) {
+      if (j < taps) {
+        const int pp = p - taps + 1 + j;
+        float v = 0.f;
+        if (pp >= ctx) v = h[(size_t)(t - (p - pp)) * W + c];                          // a row of this step
+        else if (pp >= 0) v = hist[(size_t)(pp - ctx + taps - 1) * W + c];             // a row of an earlier step
+        past[j] = v;
+      }
+    }
+    const float cur = past[taps - 1];
+    for (int k = 0; k < cn.n_out; ++k) {
+      const float* w = cn.w[k] + (size_t)c * taps;
+      float acc = cur;
+#pragma unroll
+      for (int j = 0; j < kMaxTaps; ++j)
+        if (j < taps) acc = fmaf(w[j], past[j], acc);
+      elem<OT>::store(reinterpret_cast<OT*>(cn.out[k]) + (size_t)t * W + c, acc);
+    }
+  }
+}
+
+// one CTA row per sequence: state[s] <- h of position ctx + n - (taps - 1) + s
+__global__ void __launch_bounds__(256) canon_state_kernel(const pieh_canon cn, const float* h, int W, const pieh_batch b) {
+  pdl_sync();
+  const int i = blockIdx.y;
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= W) return;
+  const int start = b.seq_start[i], n = b.seq_len[i], ctx = b.seq_ctx[i], taps = cn.taps;
+  float* hist = cn.state + (size_t)b.seq_slot[i] * (taps - 1) * W;
+  float keep[kMaxTaps];
+#pragma unroll
+  for (int s = 0; s < kMaxTaps - 1; ++s) {
+    if (s < taps - 1) {
+      const int pp = ctx + n - (taps - 1) + s;
+      float v = 0.f;
+      if (pp >= ctx) v = h[(size_t)(start + pp - ctx) * W + c];
+      else if (pp >= 0) v = hist[(size_t)(pp - ctx + taps - 1) * W + c];
+      keep[s] = v;
+    }
+  }
+#pragma unroll
+  for (int s = 0; s < kMaxTaps - 1; ++s)
+    if (s < taps - 1) hist[(size_t)s * W + c] = keep[s];
+}
+
+template <typename OT>
+__global__ void __launch_bounds__(64) mingru_scan_kernel(OT* out, const float* proj, long long ld, int width, float* state,
+                                                         const pieh_batch b) {
+  pdl_sync();
+  const int i = blockIdx.y;
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= width) return;
+  const int start = b.seq_start[i], n = b.seq_len[i];
+  float* sp = state + (size_t)b.seq_slot[i] * width + c;
+  float S = b.seq_ctx[i] > 0 ? *sp : 0.f;
+  constexpr int RUN = 8;
+  for (int r0 = 0; r0 < n; r0 += RUN) {
+    float keep[RUN], add[RUN], gate[RUN];
+#pragma unroll
+    for (int r = 0; r < RUN; ++r) {
+      if (r0 + r < n) {
+        const float* row = proj + (size_t)(start + r0 + r) * ld + c;
+        const float z = 1.f / (1.f + expf(-row[0]));
+        const float u = row[width];
+        const float cand = u >= 0.f ? u + 0.5f : 1.f / (1.f + expf(-u));
+        keep[r] = 1.f - z;
+        add[r] = z * cand;
+        gate[r] = silu_f(row[2 * (size_t)width]);
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < RUN; ++r) {
+      if (r0 + r < n) {
+        S = fmaf(keep[r], S, add[r]);
+        elem<OT>::store(out + (size_t)(start + r0 + r) * width + c, S * gate[r]);
+      }
+    }
+  }
+  *sp = S;
+}
+
+template <typename OT, typename KT>
+__global__ void __launch_bounds__(256) latent_prepare_kernel(OT* cq_out, const float* proj, long long ld, int q_rank,
+                                                             long long kv_off, int kv_rank, const float* q_norm,
+                                                             const float* kv_norm, float eps, KT* pages, const pieh_batch b) {
+  __shared__ float red[33];
+  pdl_sync();
+  const int t = blockIdx.x;
+  const int i = b.tok_seq[t], p = b.tok_pos[t];
+  const float* row = proj + (size_t)t * ld;
+  float ss = 0.f;
+  for (int c = threadIdx.x; c < q_rank; c += blockDim.x) ss = fmaf(row[c], row[c], ss);
+  const float iq = 1.f / sqrtf(block_sum(ss, red) / (float)q_rank + eps);
+  ss = 0.f;
+  for (int c = threadIdx.x; c < kv_rank; c += blockDim.x) ss = fmaf(row[kv_off + c], row[kv_off + c], ss);
+  const float ik = 1.f / sqrtf(block_sum(ss, red) / (float)kv_rank + eps);
+  for (int c = threadIdx.x; c < q_rank; c += blockDim.x) elem<OT>::store(cq_out + (size_t)t * q_rank + c, row[c] * iq * q_norm[c]);
+  const size_t slot = (size_t)b.block_table[(size_t)i * b.bt_stride + p / kPageTokens] * kPageTokens + p % kPageTokens;
+  for (int c = threadIdx.x; c < kv_rank; c += blockDim.x)
+    elem<KT>::store(pages + slot * kv_rank + c, row[kv_off + c] * ik * kv_norm[c]);
+}
+
+__global__ void rot_table_kernel(float* cs, const int32_t* positions, const double* freqs, int half, long long n) {
+  pdl_sync();
+  const long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (e >= n) return;
+  const long long t = e / half;
+  const int i = (int)(e - t * half);
+  double s, c;
+  sincos((double)positions[t] * freqs[i], &s, &c);
+  cs[2 * e] = (float)c;
+  cs[2 * e + 1] = (float)s;
+}
+
+}  // namespace pieh
+
+using namespace pieh;
+
+extern "C" int pieh_embed_scaled(float* x, const void* table, int table_dtype, const int32_t* tokens, float scale, int T,
+                                 int W, int vocab, void* stream) {
+  if (!x || !table || !tokens) return PIE_ENULL;
+  if (T < 0 || W < 1 || vocab < 1) return PIE_EINVAL_SHAPE;
+  if (T == 0) return PIE_OK;
+  count_launch();
+  PIEH_DISPATCH_DTYPE(table_dtype, ET, launch_k(embed_scaled_kernel<ET>, dim3(T), dim3(256), 0, (cudaStream_t)stream, x,
+                                                (const ET*)table, tokens, scale, W, vocab));
+  return status_of(cudaGetLastError());
+}
+
+extern "C" int pieh_residual_norm(float* x, const float* y, const pieh_mix_sum* mix, float* h, const float* norm_w,
+                                  float eps, int T, int W, void* stream) {
+  if (!x) return PIE_ENULL;
+  if (mix && mix->parts && (!mix->part_row || !mix->part_w || mix->top < 1)) return PIE_ENULL;
+  if (T < 0 || W < 1 || (size_t)W * 4 > 200 * 1024) return PIE_EINVAL_SHAPE;
+  if (T == 0) return PIE_OK;
+  pieh_mix_sum m = {};
+  if (mix && mix->parts) m = *mix;
+  const size_t smem = (size_t)W * 4;
+  if (smem > 48 * 1024) cudaFuncSetAttribute(residual_norm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  count_launch();
+  launch_k(residual_norm_kernel, dim3(T), dim3(256), smem, (cudaStream_t)stream, x, y, m, h, norm_w, eps, W);
+  return status_of(cudaGetLastError());
+}
+
+extern "C" int pieh_canon_conv(const pieh_canon* c, int out_dtype, const float* h, int W, const pieh_batch* b, void* stream) {
+  if (!c || !h || !b) return PIE_ENULL;
+  if (c->taps < 1 || c->taps > kMaxTaps || c->n_out < 1 || c->n_out > 4 || W < 1) return PIE_EINVAL_SHAPE;
+  for (int k = 0; k < c->n_out; ++k)
+    if (!c->w[k] || !c->out[k]) return PIE_ENULL;
+  if (c->taps > 1 && !c->state) return PIE_ENULL;
+  if (b->T == 0) return PIE_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  count_launch();
+  PIEH_DISPATCH_DTYPE(out_dtype, OT, launch_k(canon_kernel<OT>, dim3(b->T), dim3(256), 0, st, *c, h, W, *b));
+  cudaError_t e = cudaGetLastError();
+  if (e == cudaSuccess && c->taps > 1) {
+    count_launch();
+    e = launch_k(canon_state_kernel, dim3((W + 255) / 256, b->n_seq), dim3(256), 0, st, *c, h, W, *b);
+  }
+  return status_of(e);
+}
+
+extern "C" int pieh_mingru_scan(void* out, int out_dtype, const float* proj, long long ld, int width, float* state,
+                                const pieh_batch* b, void* stream) {
+  if (!out || !proj || !state || !b) return PIE_ENULL;
+  if (width < 1 || ld < 3LL * width) return PIE_EINVAL_SHAPE;
+  if (b->T == 0) return PIE_OK;
+  count_launch();
+  PIEH_DISPATCH_DTYPE(out_dtype, OT, launch_k(mingru_scan_kernel<OT>, dim3((width + 63) / 64, b->n_seq), dim3(64), 0,
+                                              (cudaStream_t)stream, (OT*)out, proj, ld, width, state, *b));
+  return status_of(cudaGetLastError());
+}
+
+extern "C" int pieh_latent_prepare(void* cq_out, int out_dtype, const float* proj, long long ld, int q_rank, long long kv_off,
+                                   int kv_rank, const float* q_norm, const float* kv_norm, float eps, void* pages,
+                                   int kv_dtype, const pieh_batch* b, void* stream) {
+  if (!cq_out || !proj || !q_norm || !kv_norm || !pages || !b) return PIE_ENULL;
+  if (q_rank < 1 || kv_rank < 1 || kv_off < 0) return PIE_EINVAL_SHAPE;
+  if (b->T == 0) return PIE_OK;
+  count_launch();
+  PIEH_DISPATCH_DTYPE(out_dtype, OT, PIEH_DISPATCH_DTYPE(kv_dtype, KT,
+      launch_k(latent_prepare_kernel<OT, KT>, dim3(b->T), dim3(256), 0, (cudaStream_t)stream, (OT*)cq_out, proj, ld, q_rank,
+               kv_off, kv_rank, q_norm, kv_norm, eps, (KT*)pages, *b)));
+  return status_of(cudaGetLastError());
+}
+
+extern "C" int pieh_rot_table(float* cs, const int32_t* positions, const double* freqs, int T, int half, void* stream) {
+  if (!cs || !positions || !freqs) return PIE_ENULL;
+  if (T < 0 || half < 1) return PIE_EINVAL_SHAPE;
+  if (T == 0) return PIE_OK;
+  const long long n = (long long)T * half;
+  count_launch();
+  launch_k(rot_table_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, (cudaStream_t)stream, cs, positions, freqs, half, n);
+  return status_of(cudaGetLastError());
+}

@@ -99,7 +99,8 @@ __device__ __forceinline__ void umma_store(const LinArgs& a, int m, int n0, cons
       if (n0 + 2 * q + 1 < a.N) elem<OT>::store(dst + q, y[q]);
     return;
   }
-  OT* dst = reinterpret_cast<OT*>(a.out) + (size_t)m * a.out_ld;
+  OT* dst = reinterpret_cast<OT*>(a.out) + (size_t)blockIdx.z * a.out_bs + (size_t)m * a.out_ld;
+  const float* gate = a.epi == PIEH_EPI_SIGMUL ? a.gate + (size_t)blockIdx.z * a.gate_bs + (size_t)m * a.gate_ld : nullptr;
   float y[32];
 #pragma unroll
   for (int q = 0; q < 32; ++q) {
@@ -108,6 +109,7 @@ __device__ __forceinline__ void umma_store(const LinArgs& a, int m, int n0, cons
     if (a.bias && n < a.N) t += a.bias[n];
     if (a.epi == PIEH_EPI_RELU2) { t = fmaxf(t, 0.f); t = t * t; }
     else if (a.epi == PIEH_EPI_SOFTCAP) t = a.epi_a * tanhf(t / a.epi_a);
+    else if (a.epi == PIEH_EPI_SIGMUL && n < a.N) t *= 1.f / (1.f + __expf(-gate[n]));
     y[q] = t;
   }
   if (n0 + 32 <= a.N && (reinterpret_cast<uintptr_t>(dst + n0) & 15) == 0) {
@@ -147,7 +149,7 @@ __global__ void __launch_bounds__(kThreads, 1) linear_umma_kernel(const __grid_c
   const uint32_t smA = base, smB = base + S * A_STAGE;
   const int n0 = blockIdx.x * kBN;
   int m0 = blockIdx.y * BM, m_end = a.M;
-  const __nv_bfloat16* wmat = reinterpret_cast<const __nv_bfloat16*>(a.w);
+  const __nv_bfloat16* wmat = reinterpret_cast<const __nv_bfloat16*>(a.w) + (size_t)blockIdx.z * a.w_bs;
   if (a.g_tiles) {   // grouped: this CTA's rows are one expert's run of slots (the whole CTA leaves before anything is set up)
     if ((int)blockIdx.y >= a.g_tiles[0]) return;
     const int32_t* tl = a.g_tiles + 1 + 3 * blockIdx.y;
@@ -178,7 +180,8 @@ __global__ void __launch_bounds__(kThreads, 1) linear_umma_kernel(const __grid_c
     const uint32_t swz = (uint32_t)(t & 7);
     const __nv_bfloat16* wsrc = wmat + (size_t)min(n0 + t, a.N - 1) * a.K;
     const int xslot = min(m0 + min(t, BM - 1), m_end - 1);
-    const __nv_bfloat16* xsrc = reinterpret_cast<const __nv_bfloat16*>(a.x) + (size_t)(a.g_rows ? a.g_rows[xslot] : xslot) * a.x_ld;
+    const __nv_bfloat16* xsrc = reinterpret_cast<const __nv_bfloat16*>(a.x) + (size_t)blockIdx.z * a.x_bs +
+                                (size_t)(a.g_rows ? a.g_rows[xslot] : xslot) * a.x_ld;
     bool alive = true;
     for (int kb = 0; kb < nk + LAG && alive; ++kb) {
       if (kb < nk) {
@@ -251,6 +254,7 @@ bool linear_umma_ok(const LinArgs& a, int x_dtype, int w_dtype) {
   if (!a.g_tiles && a.N <= 32 && a.K % 8 == 0 && (reinterpret_cast<uintptr_t>(a.w) & 31) == 0 &&
       (reinterpret_cast<uintptr_t>(a.x) & 31) == 0 && a.epi != PIEH_EPI_GLU)
     return false;   // a handful of output columns: linear_skinny_kernel reads x once instead of filling 256-column tiles
+  if (a.x_bs % 8 || a.w_bs % 8) return false;   // every product's operands start on a 16-byte boundary
   return x_dtype == PIE_DTYPE_BF16 && w_dtype == PIE_DTYPE_BF16 && a.M > 32 && a.K % kBK == 0 && a.x_ld % 8 == 0 &&
          (reinterpret_cast<uintptr_t>(a.x) & 15) == 0 && (reinterpret_cast<uintptr_t>(a.w) & 15) == 0;
 }
@@ -267,7 +271,7 @@ static cudaError_t launch_bm(const LinArgs& a, cudaStream_t st) {
     configured |= 1ull << (dev & 63);
   }
   // grouped: blockIdx.y walks the list of <= 128-slot tiles, whose length is only known on the device (S = experts)
-  const dim3 grid((a.N + kBN - 1) / kBN, a.g_tiles ? a.M / 128 + a.S : (a.M + BM - 1) / BM);
+  const dim3 grid((a.N + kBN - 1) / kBN, a.g_tiles ? a.M / 128 + a.S : (a.M + BM - 1) / BM, a.nb);
   count_launch();
   linear_umma_kernel<BM, S, OT><<<grid, kThreads, smem, st>>>(a);
   return cudaGetLastError();
@@ -276,7 +280,7 @@ static cudaError_t launch_bm(const LinArgs& a, cudaStream_t st) {
 cudaError_t launch_linear_umma(const LinArgs& a, int out_dtype, cudaStream_t st) {
   // 256-row tiles halve the weight traffic per flop and measured faster down to half a wave of tiles (M 2048 x N 4096:
   // 390 against 262 TFLOP/s); below that the 128-row tiles spread the work over more SMs
-  const long long tiles256 = (long long)((a.N + kBN - 1) / kBN) * ((a.M + 255) / 256);
+  const long long tiles256 = (long long)((a.N + kBN - 1) / kBN) * ((a.M + 255) / 256) * a.nb;
   static const int force = [] { const char* e = getenv("PIE_HYBRID_UMMA_TILE"); return e ? atoi(e) : 0; }();   // tuning
   int variant = a.M > 128 && 2 * tiles256 >= num_sms() ? 256 : 128;
   if (force == 128 || force == 256) variant = force;

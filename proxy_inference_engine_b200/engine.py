@@ -1,5 +1,5 @@
 """Continuous-batching engine for models that step over ``ragged.BatchDetails`` with a ``cache.HybridCache``
-(``golitar.GolitarModel``, ``babodra.BabodraModel``): the generate loop of PIE (PIE/engine/inference_engine.py:228-297) lifted from one sequence to
+(``golitar.GolitarModel``, ``babodra.BabodraModel``, ``maginex.MaginexModel``): the generate loop of PIE (PIE/engine/inference_engine.py:228-297) lifted from one sequence to
 a changing set of them.
 
     eng = HybridEngine(model, max_tokens=4096, max_seqs=4)
@@ -96,7 +96,7 @@ class _DecodeGraph:
                 layer[k].copy_(v)
 
     def snapshot(self):
-        self._saved = [{k: v.clone() for k, v in layer.items() if k in ("state", "conv")} for layer in self.cache.layers]
+        self._saved = [{k: v.clone() for k, v in layer.items() if k in self.cache.slot_keys} for layer in self.cache.layers]
 
 
 class HybridEngine:
