@@ -1,8 +1,9 @@
-"""Throughput of the Golitar and Babodra families at layer sizes of real models (random weights), with every operator of
-the step timed in place and set against its roofline.  Golitar is shown beside the quantized Llama path at equal width /
-feed-forward / depth; Babodra beside Golitar at equal width / depth / active feed-forward size.
+"""Throughput of the Golitar, Babodra and Maginex families at layer sizes of real models (random weights), with every
+operator of the step timed in place and set against its roofline.  Golitar is shown beside the quantized Llama path at
+equal width / feed-forward / depth; Babodra beside Golitar, and Maginex beside Babodra, at equal width / depth / active
+feed-forward size.
 
-``run(size, ...)`` is what ``bench.py --family golitar|babodra`` prints.  Method: one prompt of ``prompt`` tokens goes through
+``run(size, ...)`` is what ``bench.py --family golitar|babodra|maginex`` prints.  Method: one prompt of ``prompt`` tokens goes through
 ``HybridEngine.forward`` in portions of ``portion`` rows (prefill tok/s, CUDA events around all portions), then ``batch``
 sequences decode ``steps`` tokens each (decode tok/s).  The per-operator table wraps every library call of one prefill
 portion and one decode step in a CUDA event pair; bytes and flops are the algorithmic ones of the call's shapes, the
@@ -21,11 +22,15 @@ SIZES = {
     "1b": dict(width=2048, ff=8192, vocab=32000, pattern="dddadddadddadddA", dH=16, dG=16, dk=128, dv=128, aH=16, aG=4,
                ad=64, adv=128, window=1024, bab=dict(heads=16, kv_heads=4, dim=128, pattern="dmmmdmmmdmmmdmmm", experts=16, top=4,
                                                      groups=(4, 2), expert_ff=1536, shared_ff=2048),
+               mag=dict(pattern="almalmalmalmalma", heads=16, kv_heads=4, dim=128, vdim=128, window=1024, rot_dims=64,
+                        q_rank=768, kv_rank=128, gru=4096, experts=16, top=4, expert_ff=1536, shared_ff=2048, taps=4),
                llama=dict(hidden_size=2048, intermediate_size=8192, num_attention_heads=32,
                                                        num_key_value_heads=8, head_dim=64, vocab_size=32000)),
     "8b": dict(width=4096, ff=14336, vocab=32000, pattern="dddadddA", dH=32, dG=16, dk=128, dv=128, aH=32, aG=8, ad=64,
                adv=128, window=2048, bab=dict(heads=32, kv_heads=8, dim=128, pattern="dmmmdmmm", experts=16, top=4, groups=(4, 2),
                                               expert_ff=3072, shared_ff=2048),
+               mag=dict(pattern="almalmal", heads=32, kv_heads=8, dim=128, vdim=128, window=2048, rot_dims=64, q_rank=1536,
+                        kv_rank=128, gru=8192, experts=16, top=4, expert_ff=3072, shared_ff=2048, taps=4),
                llama=dict(hidden_size=4096, intermediate_size=14336, num_attention_heads=32,
                                                 num_key_value_heads=8, head_dim=128, vocab_size=32000)),
 }
@@ -63,6 +68,24 @@ def babodra_config(size: str, max_positions: int = 8192) -> dict:
     layers = [{"type": "attention", "mixer": dict(mixer), "mlp": dict(dense if ch == "d" else moe)} for ch in b["pattern"]]
     return {"architecture": "Babodra", "vocab": s["vocab"], "width": s["width"], "max_positions": max_positions,
             "norm": {"eps": 1e-5}, "layers": layers}
+
+
+def maginex_config(size: str) -> dict:
+    """Same width and depth as the other two; every layer carries a mixture with the ACTIVE size of babodra_config's
+    (top x expert ff + shared ff); mixers alternate attention / latent attention / minGRU."""
+    s = SIZES[size]
+    m = s["mag"]
+    moe = {"kind": "moe", "expert": {"ff": m["expert_ff"]}, "shared": {"ff": m["shared_ff"]},
+           "router": {"experts": m["experts"], "top": m["top"]}}
+    mixers = {"a": ("attention", {"heads": m["heads"], "kv_heads": m["kv_heads"], "dim": m["dim"], "vdim": m["vdim"],
+                                  "scale": m["dim"] ** -0.5, "mask": {"size": m["window"]}, "v_mix": True,
+                                  "rot": {"base": 5e5, "dims": m["rot_dims"]}}),
+              "l": ("latent_attention", {"heads": m["heads"], "dim": m["dim"], "vdim": m["vdim"], "q_rank": m["q_rank"],
+                                         "kv_rank": m["kv_rank"], "scale": m["dim"] ** -0.5}),
+              "m": ("mingru", {"width": m["gru"]})}
+    layers = [{"type": mixers[ch][0], "mixer": dict(mixers[ch][1]), "mlp": dict(moe)} for ch in m["pattern"]]
+    return {"architecture": "Maginex", "vocab": s["vocab"], "width": s["width"], "norm": {"eps": 1e-5},
+            "embedding": {"scale": 8.0}, "canon": {"taps": m["taps"]}, "layers": layers}
 
 
 def _peaks(root):
@@ -117,6 +140,26 @@ def _cost(name, a, model, batch_info):
         ob = 4 if a[1] == 1 else 2
         wb = 4 if a[7] == 1 else 2
         return min(E, P) * N * K * wb + P * K * act + P * (N // 2 if glu else N) * ob, 2.0 * P * N * K, f"moe_linear P={P}"
+    if name == "pieh_linear_batched":
+        nb, M, N, K = a[11], a[12], a[13], a[14]
+        ob = 4 if a[1] == 1 else 2
+        wb = 4 if a[9] == 1 else 2
+        return nb * (N * K * wb + M * K * act + M * N * ob), 2.0 * nb * M * N * K, f"linear_batched M={M} N={N} K={K}"
+    if name == "pieh_embed_scaled":
+        return a[5] * a[6] * (act + 4), 0.0, "embed"
+    if name == "pieh_residual_norm":
+        Tn, W, mix = a[6], a[7], a[2]
+        parts = mix._obj.top if mix is not None else 0
+        return Tn * W * 4 * (parts + 2 + (1 if a[3] is not None else 0)), 0.0, "residual_norm" + ("(mixture)" if parts else "")
+    if name == "pieh_canon_conv":
+        cn = a[0]._obj
+        return T * a[3] * (4 + cn.n_out * act), 2.0 * T * a[3] * cn.n_out * cn.taps, "canon_conv"
+    if name == "pieh_mingru_scan":
+        return T * a[4] * (12 + act), 0.0, "mingru_scan"
+    if name == "pieh_latent_prepare":
+        return T * (a[4] + a[6]) * (4 + act), 0.0, "latent_prepare"
+    if name == "pieh_rot_table":
+        return a[3] * a[4] * 8, 0.0, "rot_table"
     if name == "pieh_moe_route":
         pl = a[2]._obj
         return a[3] * (pl.E * 4 + pl.top * 16 * 2), 0.0, "moe_route"
@@ -131,10 +174,16 @@ def _cost(name, a, model, batch_info):
         H, G, d, dv = at.H, at.G, at.d, at.dv
         if name == "pieh_bias_attn_prepare":
             return T * ((H * d + G * d + G * dv + H * d) * 4 + G * (d + dv) * act), 0.0, "attn_prepare"
-        keys = ctx + T // max(n_seq, 1)
-        per_q = ctx + (T // max(n_seq, 1) + 1) / 2 if T > n_seq else keys
-        return (n_seq * keys * G * (d + dv) * act + T * H * (d * 4 + dv * (act + 4)), 2.0 * T * H * per_q * (d + dv),
-                "attn_run")
+        own = T // max(n_seq, 1)
+        keys = ctx + own
+        per_q = ctx + (own + 1) / 2 if T > n_seq else keys
+        if at.window:       # a query sees at most `window` keys; the step reads the pages its first row's window reaches
+            per_q = min(per_q, at.window)
+            keys = min(keys, at.window + own)
+        shared_kv = 1 if at.k_pages == at.v_pages else 2      # latent attention: keys and values are one pool
+        kvb = n_seq * keys * G * (d + dv) * act // (2 if shared_kv == 1 else 1)
+        return (kvb + T * H * (d * 4 + dv * (act + 4)), 2.0 * T * H * per_q * (d + dv),
+                "attn_run" + (f"(window {at.window})" if at.window else "") + ("(latent)" if shared_kv == 1 else ""))
     if name in ("pieh_stream_norm",):
         R, S, W = a[8], a[9], a[10]
         return R * S * W * 4 + R * W * act, 0.0, "stream_norm"
@@ -182,7 +231,16 @@ def run(size="1b", prompt=4096, portion=4096, batch=4, steps=32, warmup=3, root=
 
     hbm, tfl, src = _peaks(root)
     t0 = time.time()
-    if family == "babodra":
+    if family == "maginex":
+        from .maginex import MaginexArgs, MaginexModel, random_weights
+        cfg = maginex_config(size)
+        args = MaginexArgs.from_dict(cfg)
+        weights = random_weights(args, seed=0, device="cuda")
+        n_params = sum(v.numel() for v in weights.values())
+        model = MaginexModel(args, weights, "cuda", "bfloat16")
+        del weights
+        pattern = SIZES[size]["mag"]["pattern"]
+    elif family == "babodra":
         from .babodra import BabodraArgs, BabodraModel, random_weights
         cfg = babodra_config(size, max_positions=prompt + steps + warmup + 64)
         args = BabodraArgs.from_dict(cfg)
@@ -252,7 +310,11 @@ def run(size="1b", prompt=4096, portion=4096, batch=4, steps=32, warmup=3, root=
            "pipeline_error": int(timed._lib.pieh_pipeline_error()), "setup_s": round(time.time() - t0, 1)}
     del eng, model
     torch.cuda.empty_cache()
-    if family == "babodra":
+    if family == "maginex":
+        if with_llama:      # the closest model of the framework (sink attention + mixture of experts) at the same sizes
+            out["babodra_equal_size"] = run(size, prompt, portion, batch, steps, warmup, root, with_llama=False,
+                                            family="babodra")
+    elif family == "babodra":
         if with_llama:      # the closest model of the framework at the same width, depth and active feed-forward size
             out["golitar_equal_size"] = run(size, prompt, portion, batch, steps, warmup, root, with_llama=False)
     elif with_llama:

@@ -134,7 +134,7 @@ def forward(cfg, weights, tokens, trace=None):
     for i, ly in enumerate(cfg["layers"]):
         p = f"l{i}."
         h = rms_norm(x, w[p + "norm1"], eps)
-        hm, hf = canon(h, w[p + "canon1"]), canon(h, w[p + "canon2"])
+        hm = canon(h, w[p + "canon1"])
         m = ly["mixer"]
         if ly["type"] == "attention":
             y, v = attention_mixer(hm, w, p + "mix.", m, v_first)
@@ -147,8 +147,31 @@ def forward(cfg, weights, tokens, trace=None):
         else:
             raise ValueError(ly["type"])
         if ly.get("mlp"):
-            y = y + moe(hf, w, p + "mlp.", ly["mlp"])
+            y = y + moe(canon(h, w[p + "canon2"]), w, p + "mlp.", ly["mlp"])
         x = x + y
         if trace is not None:
             trace.append(x.clone())
     return rms_norm(x, w["final.norm"], eps) @ w["head"].T
+
+
+def random_config(vocab=96, width=64, pattern="alm", heads=4, kv_heads=2, dim=16, vdim=24, window=6, rot_dims=8, q_rank=24,
+                  kv_rank=32, gru=40, experts=6, top=2, ff=40, shared_ff=24, taps=3, scale=4.0, mlp=True, v_mix=True):
+    """A small configuration; pattern: one letter per layer, a = attention, l = latent attention, m = minGRU."""
+    layers = []
+    for ch in pattern:
+        if ch == "a":
+            mixer = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "scale": dim ** -0.5, "v_mix": v_mix}
+            if window:
+                mixer["mask"] = {"size": window}
+            if rot_dims:
+                mixer["rot"] = {"base": 1e4, "dims": rot_dims}
+            layers.append({"type": "attention", "mixer": mixer})
+        elif ch == "l":
+            layers.append({"type": "latent_attention", "mixer": {"heads": heads, "dim": dim, "vdim": vdim, "q_rank": q_rank,
+                                                                "kv_rank": kv_rank, "scale": dim ** -0.5}})
+        else:
+            layers.append({"type": "mingru", "mixer": {"width": gru}})
+        layers[-1]["mlp"] = ({"kind": "moe", "expert": {"ff": ff}, "router": {"experts": experts, "top": top},
+                              "shared": {"ff": shared_ff} if shared_ff else None} if mlp else None)
+    return {"architecture": "Maginex", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "embedding": {"scale": scale},
+            "canon": {"taps": taps}, "layers": layers}
