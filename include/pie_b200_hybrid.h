@@ -260,8 +260,10 @@ int pieh_canon_conv(const pieh_canon* c, int out_dtype, const float* h, int W, c
 /* ---- minGRU: a gated recurrence whose gates read the current token only ------------------------------------------------
  * proj fp32 [T, ld]: columns [z logits | u | gate], `width` each.  z = sigmoid(.), candidate = u + 1/2 (u >= 0) or
  * sigmoid(u) (u < 0), S_t = (1 - z) S_(t-1) + z candidate per channel, out[t, :] = S_t * silu(gate).  state fp32
- * [slots, width]: read unless the sequence has no context, written back at the end. */
-int pieh_mingru_scan(void* out, int out_dtype, const float* proj, long long ld, int width, float* state,
+ * [slots, width]: read unless the sequence has no context, written back at the end.  scratch: fp32 [3, n_tiles, width], used
+ * when a sequence brings more than 64 rows (the batch's tile list cuts them into runs that are scanned in parallel); NULL:
+ * always the one-pass kernel. */
+int pieh_mingru_scan(void* out, int out_dtype, const float* proj, long long ld, int width, float* state, float* scratch,
                      const pieh_batch* b, void* stream);
 
 /* ---- latent attention: the cached latent and the query latent ------------------------------------------------------------

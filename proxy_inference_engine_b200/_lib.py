@@ -219,7 +219,7 @@ HYBRID_SIGNATURES = {
     "pieh_embed_scaled": (_i, [_vp, _vp, _i, _vp, _f, _i, _i, _i, _vp]),
     "pieh_residual_norm": (_i, [_vp, _vp, _PMS, _vp, _vp, _f, _i, _i, _vp]),
     "pieh_canon_conv": (_i, [_PCN, _i, _vp, _i, _PB, _vp]),
-    "pieh_mingru_scan": (_i, [_vp, _i, _vp, _ll, _i, _vp, _PB, _vp]),
+    "pieh_mingru_scan": (_i, [_vp, _i, _vp, _ll, _i, _vp, _vp, _PB, _vp]),
     "pieh_latent_prepare": (_i, [_vp, _i, _vp, _ll, _i, _ll, _i, _vp, _vp, _f, _vp, _i, _PB, _vp]),
     "pieh_moe_route": (_i, [_vp, _ll, _PMP, _i, _vp]),
     "pieh_moe_linear": (_i, [_vp, _i, _ll, _vp, _i, _ll, _vp, _i, _ll, _i, _i, _i, _i, _i, _f, _f, _f, _PMP, _vp]),

@@ -5,8 +5,8 @@
 //   canon_kernel           out_k[t] = h[t] + causal per-channel convolution of h (several tap sets over one h); rows before
 //                          the step come from the sequence's state slot, rows before the sequence are zero
 //   canon_state_kernel     afterwards: the last taps - 1 rows of h of every sequence become its state
-//   mingru_scan_kernel     S_t = (1 - z_t) S_(t-1) + z_t c_t per channel, a thread per channel walking the sequence's rows
-//                          in runs of 8 whose loads and gate arithmetic do not wait for the recurrence
+//   mingru_*_kernel        S_t = (1 - z_t) S_(t-1) + z_t c_t per channel: one pass for short sequences, three passes over
+//                          64-row tiles for long portions (a tile is a linear map of its incoming state)
 //   latent_prepare_kernel  the two RMS norms of latent attention: query latent -> act tensor, key / value latent -> pages
 //   rot_table_kernel       (cos, sin) of every row's rotation angles, formed once per step for all layers that share them
 #include "hyb_common.cuh"
@@ -90,6 +90,82 @@ __global__ void __launch_bounds__(256) canon_kernel(const pieh_canon cn, const f
   }
 }
 
+__device__ __forceinline__ void store4(float* p, const float (&v)[4]) { *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]); }
+__device__ __forceinline__ void store4(__nv_bfloat16* p, const float (&v)[4]) {
+  const __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1]), c = __floats2bfloat162_rn(v[2], v[3]);
+  *reinterpret_cast<uint2*>(p) = make_uint2(*reinterpret_cast<const uint32_t*>(&a), *reinterpret_cast<const uint32_t*>(&c));
+}
+
+// W a multiple of 4: a thread owns 4 neighbouring channels and walks kCanonRows consecutive rows of the step with the last
+// taps - 1 rows of h in registers, so h is read once (plus the warm-up rows of a tile); its taps stay in registers too.
+// Where a row starts another sequence (or the tile) the window is fetched anew: this step's rows, the state slot, or zeros.
+constexpr int kCanonRows = 16;
+template <typename OT>
+__global__ void __launch_bounds__(128) canon_rows_kernel(const pieh_canon cn, const float* h, int W, const pieh_batch b) {
+  pdl_sync();
+  const int c = (blockIdx.x * 128 + threadIdx.x) * 4;
+  if (c >= W) return;
+  const int t0 = blockIdx.y * kCanonRows, t1 = min(b.T, t0 + kCanonRows);
+  const int taps = cn.taps;
+  float wt[4][kMaxTaps][4];   // [tap set][tap][channel]
+#pragma unroll
+  for (int k = 0; k < 4; ++k)
+    if (k < cn.n_out)
+#pragma unroll
+      for (int j = 0; j < kMaxTaps; ++j)
+        if (j < taps)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) wt[k][j][e] = cn.w[k][(size_t)(c + e) * taps + j];
+  float past[kMaxTaps][4];    // past[j]: h of the row's position - (taps - 1) + j, j < taps - 1
+  int prev = -1;
+  for (int t = t0; t < t1; ++t) {
+    const int i = b.tok_seq[t];
+    if (i != prev) {
+      const int p = b.tok_pos[t], ctx = b.seq_ctx[i];
+      const float* hist = cn.state + (size_t)b.seq_slot[i] * (taps - 1) * W;
+#pragma unroll
+      for (int j = 0; j < kMaxTaps - 1; ++j) {
+        if (j < taps - 1) {
+          const int pp = p - taps + 1 + j;
+          float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+          if (pp >= ctx) v = *reinterpret_cast<const float4*>(h + (size_t)(t - (p - pp)) * W + c);
+          else if (pp >= 0) v = *reinterpret_cast<const float4*>(hist + (size_t)(pp - ctx + taps - 1) * W + c);
+          past[j][0] = v.x; past[j][1] = v.y; past[j][2] = v.z; past[j][3] = v.w;
+        }
+      }
+      prev = i;
+    }
+    const float4 cv = *reinterpret_cast<const float4*>(h + (size_t)t * W + c);
+    const float cur[4] = {cv.x, cv.y, cv.z, cv.w};
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      if (k < cn.n_out) {
+        float acc[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) acc[e] = cur[e];
+#pragma unroll
+        for (int j = 0; j < kMaxTaps; ++j) {
+          if (j < taps - 1) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) acc[e] = fmaf(wt[k][j][e], past[j][e], acc[e]);
+          } else if (j == taps - 1) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) acc[e] = fmaf(wt[k][j][e], cur[e], acc[e]);
+          }
+        }
+        store4(reinterpret_cast<OT*>(cn.out[k]) + (size_t)t * W + c, acc);
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < kMaxTaps - 1; ++j) {
+      if (j < taps - 1) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) past[j][e] = j + 1 < taps - 1 ? past[j + 1 < kMaxTaps ? j + 1 : j][e] : cur[e];
+      }
+    }
+  }
+}
+
 // one CTA row per sequence: state[s] <- h of position ctx + n - (taps - 1) + s
 __global__ void __launch_bounds__(256) canon_state_kernel(const pieh_canon cn, const float* h, int W, const pieh_batch b) {
   pdl_sync();
@@ -114,6 +190,16 @@ __global__ void __launch_bounds__(256) canon_state_kernel(const pieh_canon cn, c
     if (s < taps - 1) hist[(size_t)s * W + c] = keep[s];
 }
 
+// The gates of row r, from the fused projection: keep = 1 - z, add = z * candidate
+__device__ __forceinline__ void mingru_gates(const float* row, int width, float& keep, float& add) {
+  const float z = 1.f / (1.f + expf(-row[0]));
+  const float u = row[width];
+  const float cand = u >= 0.f ? u + 0.5f : 1.f / (1.f + expf(-u));
+  keep = 1.f - z;
+  add = z * cand;
+}
+
+// Short sequences (every sequence's rows fit one 64-row tile: decoding, small portions): one pass, a thread per channel.
 template <typename OT>
 __global__ void __launch_bounds__(64) mingru_scan_kernel(OT* out, const float* proj, long long ld, int width, float* state,
                                                          const pieh_batch b) {
@@ -131,11 +217,7 @@ __global__ void __launch_bounds__(64) mingru_scan_kernel(OT* out, const float* p
     for (int r = 0; r < RUN; ++r) {
       if (r0 + r < n) {
         const float* row = proj + (size_t)(start + r0 + r) * ld + c;
-        const float z = 1.f / (1.f + expf(-row[0]));
-        const float u = row[width];
-        const float cand = u >= 0.f ? u + 0.5f : 1.f / (1.f + expf(-u));
-        keep[r] = 1.f - z;
-        add[r] = z * cand;
+        mingru_gates(row, width, keep[r], add[r]);
         gate[r] = silu_f(row[2 * (size_t)width]);
       }
     }
@@ -148,6 +230,83 @@ __global__ void __launch_bounds__(64) mingru_scan_kernel(OT* out, const float* p
     }
   }
   *sp = S;
+}
+
+// Long portions: the recurrence S <- keep S + add is linear in S, so a 64-row tile acts on its incoming state as
+// S_out = A S_in + B with A = prod keep and B = the tile's own scan from zero.
+//   pass 1 (a CTA per tile and 128 channels): A and B of every tile
+//   pass 2 (a thread per sequence and channel): walks the sequence's tiles in order -> the state each tile starts from,
+//           and the sequence's new state
+//   pass 3 (as pass 1): the scan again from the true incoming state, times silu(gate), to the output
+// scratch: [3, n_tiles, width] floats (A, B, incoming state).
+constexpr int kScanRun = 8;
+__global__ void __launch_bounds__(128) mingru_tile_kernel(const float* proj, long long ld, int width, float* scratch,
+                                                          const pieh_batch b) {
+  pdl_sync();
+  const int tile = blockIdx.y;
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= width) return;
+  const int i = b.tile_seq[tile], row0 = b.tile_row[tile];
+  const int n = min(64, b.seq_start[i] + b.seq_len[i] - row0);
+  float A = 1.f, B = 0.f;
+  for (int r0 = 0; r0 < n; r0 += kScanRun) {
+    float keep[kScanRun], add[kScanRun];
+#pragma unroll
+    for (int r = 0; r < kScanRun; ++r)
+      if (r0 + r < n) mingru_gates(proj + (size_t)(row0 + r0 + r) * ld + c, width, keep[r], add[r]);
+#pragma unroll
+    for (int r = 0; r < kScanRun; ++r)
+      if (r0 + r < n) { A *= keep[r]; B = fmaf(keep[r], B, add[r]); }
+  }
+  scratch[(size_t)tile * width + c] = A;
+  scratch[((size_t)b.n_tiles + tile) * width + c] = B;
+}
+
+__global__ void __launch_bounds__(128) mingru_carry_kernel(int width, float* scratch, float* state, const pieh_batch b) {
+  pdl_sync();
+  const int i = blockIdx.y;
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= width) return;
+  int tile = 0;   // the tile list holds every sequence's tiles in sequence order
+  for (int j = 0; j < i; ++j) tile += (b.seq_len[j] + 63) / 64;
+  const int nt = (b.seq_len[i] + 63) / 64;
+  float* sp = state + (size_t)b.seq_slot[i] * width + c;
+  float S = b.seq_ctx[i] > 0 ? *sp : 0.f;
+  for (int k = 0; k < nt; ++k, ++tile) {
+    scratch[((size_t)2 * b.n_tiles + tile) * width + c] = S;
+    S = fmaf(scratch[(size_t)tile * width + c], S, scratch[((size_t)b.n_tiles + tile) * width + c]);
+  }
+  *sp = S;
+}
+
+template <typename OT>
+__global__ void __launch_bounds__(128) mingru_apply_kernel(OT* out, const float* proj, long long ld, int width,
+                                                           const float* scratch, const pieh_batch b) {
+  pdl_sync();
+  const int tile = blockIdx.y;
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= width) return;
+  const int i = b.tile_seq[tile], row0 = b.tile_row[tile];
+  const int n = min(64, b.seq_start[i] + b.seq_len[i] - row0);
+  float S = scratch[((size_t)2 * b.n_tiles + tile) * width + c];
+  for (int r0 = 0; r0 < n; r0 += kScanRun) {
+    float keep[kScanRun], add[kScanRun], gate[kScanRun];
+#pragma unroll
+    for (int r = 0; r < kScanRun; ++r) {
+      if (r0 + r < n) {
+        const float* row = proj + (size_t)(row0 + r0 + r) * ld + c;
+        mingru_gates(row, width, keep[r], add[r]);
+        gate[r] = silu_f(row[2 * (size_t)width]);
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < kScanRun; ++r) {
+      if (r0 + r < n) {
+        S = fmaf(keep[r], S, add[r]);
+        elem<OT>::store(out + (size_t)(row0 + r0 + r) * width + c, S * gate[r]);
+      }
+    }
+  }
 }
 
 template <typename OT, typename KT>
@@ -222,7 +381,13 @@ extern "C" int pieh_canon_conv(const pieh_canon* c, int out_dtype, const float* 
   if (b->T == 0) return PIE_OK;
   cudaStream_t st = (cudaStream_t)stream;
   count_launch();
-  PIEH_DISPATCH_DTYPE(out_dtype, OT, launch_k(canon_kernel<OT>, dim3(b->T), dim3(256), 0, st, *c, h, W, *b));
+  bool aligned = W % 4 == 0 && (reinterpret_cast<uintptr_t>(h) & 15) == 0 && (!c->state || (reinterpret_cast<uintptr_t>(c->state) & 15) == 0);
+  for (int k = 0; k < c->n_out; ++k) aligned = aligned && (reinterpret_cast<uintptr_t>(c->out[k]) & 15) == 0;
+  if (aligned)
+    PIEH_DISPATCH_DTYPE(out_dtype, OT, launch_k(canon_rows_kernel<OT>, dim3((W + 511) / 512, (b->T + kCanonRows - 1) / kCanonRows),
+                                                dim3(128), 0, st, *c, h, W, *b));
+  else
+    PIEH_DISPATCH_DTYPE(out_dtype, OT, launch_k(canon_kernel<OT>, dim3(b->T), dim3(256), 0, st, *c, h, W, *b));
   cudaError_t e = cudaGetLastError();
   if (e == cudaSuccess && c->taps > 1) {
     count_launch();
@@ -232,14 +397,29 @@ extern "C" int pieh_canon_conv(const pieh_canon* c, int out_dtype, const float* 
 }
 
 extern "C" int pieh_mingru_scan(void* out, int out_dtype, const float* proj, long long ld, int width, float* state,
-                                const pieh_batch* b, void* stream) {
+                                float* scratch, const pieh_batch* b, void* stream) {
   if (!out || !proj || !state || !b) return PIE_ENULL;
   if (width < 1 || ld < 3LL * width) return PIE_EINVAL_SHAPE;
   if (b->T == 0) return PIE_OK;
-  count_launch();
-  PIEH_DISPATCH_DTYPE(out_dtype, OT, launch_k(mingru_scan_kernel<OT>, dim3((width + 63) / 64, b->n_seq), dim3(64), 0,
-                                              (cudaStream_t)stream, (OT*)out, proj, ld, width, state, *b));
-  return status_of(cudaGetLastError());
+  cudaStream_t st = (cudaStream_t)stream;
+  const bool tiled = scratch && b->n_tiles > b->n_seq && b->tile_seq && b->tile_row;   // some sequence spans several tiles
+  if (!tiled) {
+    count_launch();
+    PIEH_DISPATCH_DTYPE(out_dtype, OT, launch_k(mingru_scan_kernel<OT>, dim3((width + 63) / 64, b->n_seq), dim3(64), 0, st,
+                                                (OT*)out, proj, ld, width, state, *b));
+    return status_of(cudaGetLastError());
+  }
+  count_launch(3);
+  const dim3 grid((width + 127) / 128, b->n_tiles);
+  cudaError_t e = launch_k(mingru_tile_kernel, grid, dim3(128), 0, st, proj, ld, width, scratch, *b);
+  if (e == cudaSuccess)
+    e = launch_k(mingru_carry_kernel, dim3((width + 127) / 128, b->n_seq), dim3(128), 0, st, width, scratch, state, *b);
+  if (e == cudaSuccess) {
+    PIEH_DISPATCH_DTYPE(out_dtype, OT, launch_k(mingru_apply_kernel<OT>, grid, dim3(128), 0, st, (OT*)out, proj, ld, width,
+                                                (const float*)scratch, *b));
+    e = cudaGetLastError();
+  }
+  return status_of(e);
 }
 
 extern "C" int pieh_latent_prepare(void* cq_out, int out_dtype, const float* proj, long long ld, int q_rank, long long kv_off,

@@ -155,7 +155,7 @@ def _cost(name, a, model, batch_info):
         cn = a[0]._obj
         return T * a[3] * (4 + cn.n_out * act), 2.0 * T * a[3] * cn.n_out * cn.taps, "canon_conv"
     if name == "pieh_mingru_scan":
-        return T * a[4] * (12 + act), 0.0, "mingru_scan"
+        return T * a[4] * (12 + act), 0.0, "mingru_scan"      # the projection once, the output once
     if name == "pieh_latent_prepare":
         return T * (a[4] + a[6]) * (4 + act), 0.0, "latent_prepare"
     if name == "pieh_rot_table":

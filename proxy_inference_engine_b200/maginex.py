@@ -329,8 +329,9 @@ class MaginexModel:
             else:
                 (n,) = ly["dims"]
                 mixed = self._empty((T, n), self.act_torch)
-                _lib.check_hybrid(L.pieh_mingru_scan(_p(mixed), self.act, _p(proj), ld, n, _p(st["state"]), bref, _stream()),
-                                  "mingru_scan")
+                scratch = self._empty((3, desc.n_tiles, n)) if desc.n_tiles > desc.n_seq else None
+                _lib.check_hybrid(L.pieh_mingru_scan(_p(mixed), self.act, _p(proj), ld, n, _p(st["state"]), _p(scratch), bref,
+                                                     _stream()), "mingru_scan")
             self._linear(ly["out"], mixed, T, into=x)
             mix = alive = None
             if ml:
