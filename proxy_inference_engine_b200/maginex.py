@@ -26,6 +26,7 @@ One step over a ``ragged.BatchDetails`` (x: fp32 residual [T, W]; h: fp32 normed
                   -> bias_attn_run (window, learned sink, per-head gate)
       latent:     p = linear(u1; [dq | dkv | gate])   ->  latent_prepare (two norms; latent -> pages)
                   -> q = linear(cq; uq)  ->  q~ = linear_batched(q; uk^T per head)       keys are never expanded:
+                     (kv_rank <= dim: uk^T uq is one matrix, formed at load)
                   -> bias_attn_run over the latent pages (one shared "head" of kv_rank)   (uk^T q) . c = q . (uk c)
                   -> linear_batched(.; uv per head, x sigmoid(gate))                      and uv (sum p c) = sum p (uv c)
       mingru:     p = linear(u1; [z | x | gate], biases)  ->  mingru_scan (state in the slot)
@@ -176,9 +177,15 @@ class MaginexModel:
                 ly["dims"] = (H, d, dv, rq, rkv)
                 ly["proj"] = lin(torch.cat([mw("dq"), mw("dkv"), mw("g")], 0))
                 ly["dq_norm"], ly["dkv_norm"] = f32(mw("dq.norm")), f32(mw("dkv.norm"))
-                ly["uq"] = lin(mw("uq"))
-                # per head: uk^T [kv_rank, dim] (queries go INTO the latent space) and uv [vdim, kv_rank]
-                ly["ukT"] = mw("uk").reshape(H, d, rkv).transpose(1, 2).to(device=device, dtype=wdt).contiguous()
+                # queries go INTO the latent space: per head q~ = uk^T q with uk^T [kv_rank, dim].  Where the latent is no
+                # wider than a head, uk^T uq is formed once here (one matrix of no more rows than uq: same product count,
+                # one launch fewer per step); otherwise q is formed first and the heads' uk^T follow as one batched product
+                ukT = mw("uk").reshape(H, d, rkv).transpose(1, 2)
+                if rkv <= d:
+                    fold = torch.bmm(ukT.double(), mw("uq").reshape(H, d, rq).double()).reshape(H * rkv, rq)
+                    ly["uq"], ly["ukT"] = lin(fold.float()), None
+                else:
+                    ly["uq"], ly["ukT"] = lin(mw("uq")), ukT.to(device=device, dtype=wdt).contiguous()
                 ly["uv"] = mw("uv").reshape(H, dv, rkv).to(device=device, dtype=wdt).contiguous()
                 ly["out"] = lin(mw("o"))
                 ly["sink"], ly["scale"] = f32(mw("sink")), float(m["scale"])
@@ -317,8 +324,11 @@ class MaginexModel:
                 _lib.check_hybrid(L.pieh_latent_prepare(_p(cq), self.act, _p(proj), ld, rq, rq, rkv, _p(ly["dq_norm"]),
                                                         _p(ly["dkv_norm"]), eps, _p(st["c"]), self.act, bref, _stream()),
                                   "latent_prepare")
-                qh = self._linear(ly["uq"], cq, T, out_dtype=self.act)                       # [T, H d]
-                ql = self._heads(self._empty((T, H * rkv)), DTYPE_F32, qh, ly["ukT"], T, H, rkv, d)
+                if ly["ukT"] is None:
+                    ql = self._linear(ly["uq"], cq, T)                                       # [T, H kv_rank] at once
+                else:
+                    qh = self._linear(ly["uq"], cq, T, out_dtype=self.act)                   # [T, H d]
+                    ql = self._heads(self._empty((T, H * rkv)), DTYPE_F32, qh, ly["ukT"], T, H, rkv, d)
                 at = HybBiasAttn(H, 1, rkv, rkv, 0, 0, -1, None, None, eps, ly["scale"], 0.0, 0.0, None, 0, 0, _p(st["c"]),
                                  _p(st["c"]), self.act, _p(ly["sink"]), 0, 0, None, None, None)
                 ol = self._empty((T, H * rkv), self.act_torch)

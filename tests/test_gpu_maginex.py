@@ -275,7 +275,7 @@ def test_convolution_history_crosses_portions_and_starts_empty():
     dict(shared_ff=0), dict(scale=1.0), dict(v_mix=False),
     dict(width=72, dim=12, vdim=20, rot_dims=6, q_rank=20, kv_rank=40, gru=36, ff=28, shared_ff=12, experts=5, top=3),
     dict(width=40, dim=8, vdim=8, kv_rank=8, q_rank=8, gru=8, ff=8, shared_ff=8, heads=2, kv_heads=2),
-    dict(kv_rank=320, vdim=136, heads=2, kv_heads=1), dict(width=66, gru=30, ff=18, shared_ff=10, q_rank=18, kv_rank=22, vdim=10)])
+    dict(kv_rank=320, vdim=136, heads=2, kv_heads=1), dict(kv_rank=16), dict(kv_rank=8, q_rank=40), dict(width=66, gru=30, ff=18, shared_ff=10, q_rank=18, kv_rank=22, vdim=10)])
 def test_other_sizes(kw):
     cfg, w, model = make(pattern="aalm", seed=2, **kw)
     ids = toks(75, seed=4)
