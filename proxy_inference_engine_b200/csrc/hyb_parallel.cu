@@ -100,23 +100,23 @@ __device__ __forceinline__ void store4(__nv_bfloat16* p, const float (&v)[4]) {
 // taps - 1 rows of h in registers, so h is read once (plus the warm-up rows of a tile); its taps stay in registers too.
 // Where a row starts another sequence (or the tile) the window is fetched anew: this step's rows, the state slot, or zeros.
 constexpr int kCanonRows = 16;
-template <typename OT>
+template <typename OT, int MAXT, int NOUT>   // array sizes: taps <= MAXT, tap sets <= NOUT (registers, hence occupancy)
 __global__ void __launch_bounds__(128) canon_rows_kernel(const pieh_canon cn, const float* h, int W, const pieh_batch b) {
   pdl_sync();
   const int c = (blockIdx.x * 128 + threadIdx.x) * 4;
   if (c >= W) return;
   const int t0 = blockIdx.y * kCanonRows, t1 = min(b.T, t0 + kCanonRows);
   const int taps = cn.taps;
-  float wt[4][kMaxTaps][4];   // [tap set][tap][channel]
+  float wt[NOUT][MAXT][4];   // [tap set][tap][channel]
 #pragma unroll
-  for (int k = 0; k < 4; ++k)
+  for (int k = 0; k < NOUT; ++k)
     if (k < cn.n_out)
 #pragma unroll
-      for (int j = 0; j < kMaxTaps; ++j)
+      for (int j = 0; j < MAXT; ++j)
         if (j < taps)
 #pragma unroll
           for (int e = 0; e < 4; ++e) wt[k][j][e] = cn.w[k][(size_t)(c + e) * taps + j];
-  float past[kMaxTaps][4];    // past[j]: h of the row's position - (taps - 1) + j, j < taps - 1
+  float past[MAXT][4];    // past[j]: h of the row's position - (taps - 1) + j, j < taps - 1
   int prev = -1;
   for (int t = t0; t < t1; ++t) {
     const int i = b.tok_seq[t];
@@ -124,7 +124,7 @@ __global__ void __launch_bounds__(128) canon_rows_kernel(const pieh_canon cn, co
       const int p = b.tok_pos[t], ctx = b.seq_ctx[i];
       const float* hist = cn.state + (size_t)b.seq_slot[i] * (taps - 1) * W;
 #pragma unroll
-      for (int j = 0; j < kMaxTaps - 1; ++j) {
+      for (int j = 0; j < MAXT - 1; ++j) {
         if (j < taps - 1) {
           const int pp = p - taps + 1 + j;
           float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -138,13 +138,13 @@ __global__ void __launch_bounds__(128) canon_rows_kernel(const pieh_canon cn, co
     const float4 cv = *reinterpret_cast<const float4*>(h + (size_t)t * W + c);
     const float cur[4] = {cv.x, cv.y, cv.z, cv.w};
 #pragma unroll
-    for (int k = 0; k < 4; ++k) {
+    for (int k = 0; k < NOUT; ++k) {
       if (k < cn.n_out) {
         float acc[4];
 #pragma unroll
         for (int e = 0; e < 4; ++e) acc[e] = cur[e];
 #pragma unroll
-        for (int j = 0; j < kMaxTaps; ++j) {
+        for (int j = 0; j < MAXT; ++j) {
           if (j < taps - 1) {
 #pragma unroll
             for (int e = 0; e < 4; ++e) acc[e] = fmaf(wt[k][j][e], past[j][e], acc[e]);
@@ -157,10 +157,10 @@ __global__ void __launch_bounds__(128) canon_rows_kernel(const pieh_canon cn, co
       }
     }
 #pragma unroll
-    for (int j = 0; j < kMaxTaps - 1; ++j) {
+    for (int j = 0; j < MAXT - 1; ++j) {
       if (j < taps - 1) {
 #pragma unroll
-        for (int e = 0; e < 4; ++e) past[j][e] = j + 1 < taps - 1 ? past[j + 1 < kMaxTaps ? j + 1 : j][e] : cur[e];
+        for (int e = 0; e < 4; ++e) past[j][e] = j + 1 < taps - 1 ? past[j + 1][e] : cur[e];
       }
     }
   }
@@ -272,9 +272,22 @@ __global__ void __launch_bounds__(128) mingru_carry_kernel(int width, float* scr
   const int nt = (b.seq_len[i] + 63) / 64;
   float* sp = state + (size_t)b.seq_slot[i] * width + c;
   float S = b.seq_ctx[i] > 0 ? *sp : 0.f;
-  for (int k = 0; k < nt; ++k, ++tile) {
-    scratch[((size_t)2 * b.n_tiles + tile) * width + c] = S;
-    S = fmaf(scratch[(size_t)tile * width + c], S, scratch[((size_t)b.n_tiles + tile) * width + c]);
+  for (int k0 = 0; k0 < nt; k0 += kScanRun, tile += kScanRun) {   // the loads of a run do not wait for the chain
+    float A[kScanRun], B[kScanRun];
+#pragma unroll
+    for (int k = 0; k < kScanRun; ++k) {
+      if (k0 + k < nt) {
+        A[k] = scratch[(size_t)(tile + k) * width + c];
+        B[k] = scratch[((size_t)b.n_tiles + tile + k) * width + c];
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < kScanRun; ++k) {
+      if (k0 + k < nt) {
+        scratch[((size_t)2 * b.n_tiles + tile + k) * width + c] = S;
+        S = fmaf(A[k], S, B[k]);
+      }
+    }
   }
   *sp = S;
 }
@@ -383,10 +396,15 @@ extern "C" int pieh_canon_conv(const pieh_canon* c, int out_dtype, const float* 
   count_launch();
   bool aligned = W % 4 == 0 && (reinterpret_cast<uintptr_t>(h) & 15) == 0 && (!c->state || (reinterpret_cast<uintptr_t>(c->state) & 15) == 0);
   for (int k = 0; k < c->n_out; ++k) aligned = aligned && (reinterpret_cast<uintptr_t>(c->out[k]) & 15) == 0;
-  if (aligned)
-    PIEH_DISPATCH_DTYPE(out_dtype, OT, launch_k(canon_rows_kernel<OT>, dim3((W + 511) / 512, (b->T + kCanonRows - 1) / kCanonRows),
-                                                dim3(128), 0, st, *c, h, W, *b));
-  else
+  if (aligned) {
+    const dim3 grid((W + 511) / 512, (b->T + kCanonRows - 1) / kCanonRows);
+#define PIEH_CANON(MAXT, NOUT) PIEH_DISPATCH_DTYPE(out_dtype, OT, launch_k(canon_rows_kernel<OT, MAXT, NOUT>, grid, dim3(128), 0, st, *c, h, W, *b))
+    if (c->taps <= 4 && c->n_out <= 2) PIEH_CANON(4, 2);
+    else if (c->taps <= 4) PIEH_CANON(4, 4);
+    else if (c->n_out <= 2) PIEH_CANON(8, 2);
+    else PIEH_CANON(8, 4);
+#undef PIEH_CANON
+  } else
     PIEH_DISPATCH_DTYPE(out_dtype, OT, launch_k(canon_kernel<OT>, dim3(b->T), dim3(256), 0, st, *c, h, W, *b));
   cudaError_t e = cudaGetLastError();
   if (e == cudaSuccess && c->taps > 1) {
