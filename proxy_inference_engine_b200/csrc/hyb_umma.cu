@@ -102,15 +102,25 @@ __device__ __forceinline__ void umma_store(const LinArgs& a, int m, int n0, cons
   OT* dst = reinterpret_cast<OT*>(a.out) + (size_t)blockIdx.z * a.out_bs + (size_t)m * a.out_ld;
   const float* gate = a.epi == PIEH_EPI_SIGMUL ? a.gate + (size_t)blockIdx.z * a.gate_bs + (size_t)m * a.gate_ld : nullptr;
   float y[32];
+  if (gate && n0 + 32 <= a.N && (reinterpret_cast<uintptr_t>(gate + n0) & 15) == 0) {   // the gate logits of a whole run, 16 bytes at a time
 #pragma unroll
-  for (int q = 0; q < 32; ++q) {
-    const int n = n0 + q;
-    float t = __uint_as_float(v[q]);
-    if (a.bias && n < a.N) t += a.bias[n];
-    if (a.epi == PIEH_EPI_RELU2) { t = fmaxf(t, 0.f); t = t * t; }
-    else if (a.epi == PIEH_EPI_SOFTCAP) t = a.epi_a * tanhf(t / a.epi_a);
-    else if (a.epi == PIEH_EPI_SIGMUL && n < a.N) t *= 1.f / (1.f + __expf(-gate[n]));
-    y[q] = t;
+    for (int q4 = 0; q4 < 8; ++q4) {
+      const float4 gq = *reinterpret_cast<const float4*>(gate + n0 + 4 * q4);
+      const float gl[4] = {gq.x, gq.y, gq.z, gq.w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) y[4 * q4 + e] = __uint_as_float(v[4 * q4 + e]) / (1.f + __expf(-gl[e]));
+    }
+  } else {
+#pragma unroll
+    for (int q = 0; q < 32; ++q) {
+      const int n = n0 + q;
+      float t = __uint_as_float(v[q]);
+      if (a.bias && n < a.N) t += a.bias[n];
+      if (a.epi == PIEH_EPI_RELU2) { t = fmaxf(t, 0.f); t = t * t; }
+      else if (a.epi == PIEH_EPI_SOFTCAP) t = a.epi_a * tanhf(t / a.epi_a);
+      else if (a.epi == PIEH_EPI_SIGMUL && n < a.N) t *= 1.f / (1.f + __expf(-gate[n]));
+      y[q] = t;
+    }
   }
   if (n0 + 32 <= a.N && (reinterpret_cast<uintptr_t>(dst + n0) & 15) == 0) {
     if (sizeof(OT) == 4) {
