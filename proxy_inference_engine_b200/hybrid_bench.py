@@ -79,7 +79,7 @@ def maginex_config(size: str) -> dict:
            "router": {"experts": m["experts"], "top": m["top"]}}
     mixers = {"a": ("attention", {"heads": m["heads"], "kv_heads": m["kv_heads"], "dim": m["dim"], "vdim": m["vdim"],
                                   "scale": m["dim"] ** -0.5, "mask": {"size": m["window"]}, "v_mix": True,
-                                  "rot": {"base": 5e5, "dims": m["rot_dims"]}}),
+                                  "rot": {"base": 1e6, "dims": m["rot_dims"]}}),
               "l": ("latent_attention", {"heads": m["heads"], "dim": m["dim"], "vdim": m["vdim"], "q_rank": m["q_rank"],
                                          "kv_rank": m["kv_rank"], "scale": m["dim"] ** -0.5}),
               "m": ("mingru", {"width": m["gru"]})}

@@ -190,7 +190,7 @@ def _point_a_key_at_a_query(w, cfg, q_tok, k_tok, gain):
     w["l0.mix.k"] = (gain * f("l0.mix.k")).to(torch.bfloat16)
 
 
-@pytest.mark.parametrize("window,probe", [(6, 20), (64, 64), (64, 100), (65, 130), (72, 200)])
+@pytest.mark.parametrize("window,probe", [(6, 20), (64, 64), (64, 100), (65, 130), (90, 200)])
 def test_keys_just_inside_and_just_outside_the_window(window, probe):
     """One earlier token's key points at the probe's query, just inside the window or just outside it, so a window that is
     one token off changes the logits by far more than the tolerance."""
@@ -295,6 +295,22 @@ def test_greedy_generation_through_the_scheduler():
         for k, tok in enumerate(o):                                   # each new token is the restatement's choice, or ties it
             row = logits[len(p) + k - 1]
             assert float(row.max() - row[tok]) < 1e-3 * float(row.abs().max()), (k, tok)
+
+
+def test_generate_command(tmp_path):
+    from safetensors.torch import save_file
+    cfg, w, model = make(pattern="lma")
+    (tmp_path / "config.json").write_text(json.dumps(cfg))
+    save_file({k: v.contiguous() for k, v in w.items()}, str(tmp_path / "model.safetensors"))
+    prompts = [toks(9, seed=85), toks(40, seed=86)]
+    cmd = [sys.executable, "-m", "proxy_inference_engine_b200", "generate", "--model", str(tmp_path), "--dtype", "float32",
+           "--max-new-tokens", "6"] + [x for p in prompts for x in ("--prompt-ids", ",".join(map(str, p)))]
+    r = subprocess.run(cmd, cwd=ROOT, capture_output=True, text=True, timeout=900)
+    assert r.returncode == 0, r.stderr[-2000:]
+    lines = [json.loads(ln) for ln in r.stdout.splitlines() if ln.startswith("{")]
+    assert [ln["prompt_ids"] for ln in lines] == prompts
+    want = engine(model).generate(prompts, max_new_tokens=6)
+    assert [ln["generated_ids"] for ln in lines] == want
 
 
 def test_trace_replay_program(tmp_path):
