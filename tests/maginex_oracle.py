@@ -111,10 +111,15 @@ def expert(h, w, p):
     return (a * a) @ w[p + "down"].T
 
 
-def moe(h, w, p, mlp):
+def moe(h, w, p, mlp, margins=None):
+    """margins: list that receives, per token, the gap between the last chosen logit and the best one left out (how close
+    the choice was; infinite when every expert is chosen)."""
     E, top = mlp["router"]["experts"], mlp["router"]["top"]
     z = h @ w[p + "router"].T + w[p + "router.b"]
     out = torch.zeros_like(h)
+    if margins is not None:
+        zs = torch.sort(z, dim=-1, descending=True).values
+        margins.append(zs[:, top - 1] - zs[:, top] if top < E else torch.full((h.shape[0],), float("inf"), dtype=F))
     for t in range(h.shape[0]):
         val, idx = torch.sort(z[t], descending=True, stable=True)
         wts = torch.softmax(val[:top], 0)
@@ -125,8 +130,9 @@ def moe(h, w, p, mlp):
     return out
 
 
-def forward(cfg, weights, tokens, trace=None):
-    """tokens: list of ids -> logits [L, vocab] (float64).  trace: list that receives the residual after every layer."""
+def forward(cfg, weights, tokens, trace=None, margins=None):
+    """tokens: list of ids -> logits [L, vocab] (float64).  trace: list that receives the residual after every layer;
+    margins: list that receives every routed layer's per-token routing margin."""
     w = {k: v.to(F) for k, v in weights.items()}
     eps = cfg["norm"]["eps"]
     x = w["embed"][torch.tensor(tokens)] * cfg["embedding"]["scale"]
@@ -147,7 +153,7 @@ def forward(cfg, weights, tokens, trace=None):
         else:
             raise ValueError(ly["type"])
         if ly.get("mlp"):
-            y = y + moe(canon(h, w[p + "canon2"]), w, p + "mlp.", ly["mlp"])
+            y = y + moe(canon(h, w[p + "canon2"]), w, p + "mlp.", ly["mlp"], margins)
         x = x + y
         if trace is not None:
             trace.append(x.clone())

@@ -82,10 +82,22 @@ def test_each_mixer_and_the_experts_alone(pattern, mlp):
 
 
 def test_bf16_tracks_the_restatement():
+    """In bf16 a token whose routing margin is within rounding may take another expert than the restatement, and nudges
+    the tokens after it (attention, recurrent state): rows up to the first close call must be within the tolerance, nine
+    rows in ten of all, and none far off."""
     cfg, w, model = make(pattern="almal", dtype="bfloat16")
     ids = toks(150)
-    e = rows_err(in_portions(engine(model), ids, [70, 33, 1]), O.forward(cfg, w, ids))
+    margins = []
+    e = rows_err(in_portions(engine(model), ids, [70, 33, 1]), O.forward(cfg, w, ids, None, margins))
+    clear = torch.cummin(torch.stack(margins).min(0).values, 0).values > 0.02
+    assert int(clear.sum()) >= 5 and float(e[clear].max()) < TOL16
     assert float(e.quantile(0.9)) < TOL16 and float(e.max()) < 6 * TOL16
+
+
+def test_bf16_without_routing_is_within_tolerance_everywhere():
+    cfg, w, model = make(pattern="almal", dtype="bfloat16", mlp=False)
+    ids = toks(150)
+    assert err(in_portions(engine(model), ids, [70, 33, 1]), O.forward(cfg, w, ids)) < TOL16
 
 
 @pytest.mark.parametrize("dtype,tol", [("float32", TOL32), ("bfloat16", None)])
