@@ -666,6 +666,7 @@ def run_reference(a):
 
 def run_golitar(a):
     from proxy_inference_engine_b200 import hybrid_bench
+    sampler = ClockSampler(0)        # over the whole run, model set-up included: the reasons matter more than the median
     rec = hybrid_bench.run(a.size, prompt=max(a.prompt, 4096) if a.prompt == 128 else a.prompt, batch=max(a.batch, 4)
                            if a.batch == 1 else a.batch, steps=min(a.steps, 64), warmup=max(a.warmup, 3), root=ROOT,
                            family=a.family)
@@ -674,6 +675,7 @@ def run_golitar(a):
             "higher_is_better": True, "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "gpu_launches": rec["decode"]["launches_per_step"] * min(a.steps, 64), "config": {"model": f"{a.family}-{a.size}"}}
     line.update(rec)
+    line["clocks"] = sampler.stop()
     print(json.dumps(line), flush=True)
 
 
