@@ -42,7 +42,9 @@ enum {
   PIEH_EPI_SOFTCAP = 2,  /* y <- cap * tanh(y / cap)                           */
   PIEH_EPI_STREAMS = 3,  /* out is the residual [M, S, N] fp32: x[m, t, n] <- sum_s mix[s, t] x[m, s, n] + outw[t] * y */
   PIEH_EPI_GLU = 4,      /* gated pair (pieh_linear_glu only): out [M, N / 2]                                        */
-  PIEH_EPI_SIGMUL = 5    /* y <- y * sigmoid(gate[m, n])   (pieh_linear_batched only)                                */
+  PIEH_EPI_SIGMUL = 5,   /* y <- y * sigmoid(gate[m, n])   (pieh_linear_batched only)                                */
+  PIEH_EPI_TANH = 6,     /* y <- tanh(y)                   (pieh_linear_act only)                                    */
+  PIEH_EPI_XIELU = 7     /* y <- a y^2 + y / 2 (y > 0),  b (e^y - 1 - y) + y / 2 (y <= 0)   (pieh_linear_act only)    */
 };
 
 /* ragged step descriptor, shared by the recurrent and the attention operators (all arrays int32, device) */
@@ -68,6 +70,11 @@ typedef struct pieh_batch {
 int pieh_linear(void* out, int out_dtype, long long out_ld, const void* x, int x_dtype, long long x_ld, const void* w,
                 int w_dtype, const float* bias, int M, int N, int K, int epilogue, float epi_a, const float* mix,
                 const float* outw, int S, void* stream);
+
+/* pieh_linear with an activation that takes up to two constants: NONE, RELU2, TANH, or XIELU with a = act_a, b = act_b
+ * (the caller passes the finished coefficients, e.g. softplus of learned numbers). */
+int pieh_linear_act(void* out, int out_dtype, long long out_ld, const void* x, int x_dtype, long long x_ld, const void* w,
+                    int w_dtype, const float* bias, int M, int N, int K, int act, float act_a, float act_b, void* stream);
 
 /* nb independent products in one launch (one per head, say): for z < nb
  *   out[z * out_bs + m * out_ld + n] = sum_k x[z * x_bs + m * x_ld + k] * w[z * w_bs + n * K + k]
@@ -195,6 +202,9 @@ typedef struct pieh_bias_attn {
   const float* rot_cs;     /* [T, rot_dims / 2, 2] (cos, sin) of each row's angles: pieh_rot_table */
   const float* v_mix;      /* device scalar lambda: v <- (1 - lambda) v + lambda v_keep[t] before the pages are written */
   float* v_keep;           /* [T, G dv] fp32: read when v_mix is set; otherwise, if not NULL, this call's values are left here */
+  int sigmoid;             /* 1: no softmax -- a visible key weighs sigmoid(s_ij + score_bias[h]), the weights are not normalised
+                              over the keys and there is no sink */
+  const float* score_bias; /* [H] added to the score inside the sigmoid (NULL: none) */
 } pieh_bias_attn;
 /* q_out fp32 [T, H, d]; k' and v appended to the pages at each row's position.  Rotation (after the norms) turns the pair
  * (u, v) = (x[i], x[i + rot_dims / 2]) into (u cos - v sin, v cos + u sin). */
@@ -274,6 +284,65 @@ int pieh_mingru_scan(void* out, int out_dtype, const float* proj, long long ld, 
 int pieh_latent_prepare(void* cq_out, int out_dtype, const float* proj, long long ld, int q_rank, long long kv_off,
                         int kv_rank, const float* q_norm, const float* kv_norm, float eps, void* pages, int kv_dtype,
                         const pieh_batch* b, void* stream);
+
+/* ---- sandwich-norm residual: a sublayer's output passes its own norm on the way into the residual, and the next
+ * sublayer's input norm is formed in the same pass ------------------------------------------------------------------------
+ *   x[t, :] += mult * rms_norm(y[t, :]) * post_w          y plain fp32 [T, W], or the mixture of pieh_postnorm_add (a NULL
+ *                                                          shared_gate: the shared rows count fully); skipped when both are NULL
+ *   x[t, :] += add_rows[t, :] + add_vec[:]                 each optional (a looped stack re-injects its input this way)
+ *   h[t, :]  = rms_norm(x[t, :]) * next_w                  act dtype; skipped when h or next_w is NULL */
+int pieh_sandwich_add(float* x, const float* y, const pieh_mix_sum* mix, const float* post_w, float mult,
+                      const float* add_rows, const float* add_vec, void* h, int h_dtype, const float* next_w, float eps,
+                      int T, int W, void* stream);
+
+/* out[t, c] = norm-and-gate of x[t, :] in `groups` equal parts of group_size features, each by its own root mean square:
+ *   gate_first 0:  x / rms(x) * w * f(gate)          gate_first 1:  (x f(gate)) / rms(x f(gate)) * w
+ * f: gate_fn 0 none (gate may be NULL), 1 sigmoid, 2 silu.  x fp32 row stride x_ld, gate fp32 row stride gate_ld,
+ * w [groups * group_size], out act [T, groups * group_size]. */
+int pieh_gated_group_norm(void* out, int out_dtype, const float* x, long long x_ld, const float* gate, long long gate_ld,
+                          const float* w, int groups, int group_size, float eps, int gate_fn, int gate_first, int T,
+                          void* stream);
+
+/* ---- generalized delta rule: per-channel decay and a removal term along the unit key ---------------------------------------
+ * proj fp32 [T, ld] holds r at r_off, k at k_off (H dk each), v at v_off (H dv) and the removal logits at a_off (H dk).
+ *   w = exp(-decay_scale * sigmoid(decay_logits)),  a = sigmoid(a_logits + a_bias),  u = k / sqrt(|k|^2 + key_eps)  per head
+ *   S_t = diag(w) S_(t-1) - (a * u)(u^T S_(t-1)) + k v^T      (S [dk, dv]; both corrections read the old state)
+ *   o_t = S_t^T r */
+typedef struct pieh_gdelta {
+  int H, dk, dv;
+  long long r_off, k_off, v_off, a_off;
+  const float* a_bias;   /* [H dk] or NULL */
+  float decay_scale, key_eps;
+  float* state;          /* [slots, H, dk, dv] fp32 */
+} pieh_gdelta;
+/* decay, u, au fp32 [T, H, dk]; decay_logits fp32 [T, dl_ld] (their bias already added). */
+int pieh_gdelta_prepare(float* decay, float* u, float* au, const float* proj, long long ld, const float* decay_logits,
+                        long long dl_ld, const pieh_gdelta* d, int T, void* stream);
+/* the recurrence over each sequence's rows (state from and back to its slot; no context: from zero).  o fp32 [T, H, dv]. */
+int pieh_gdelta_scan(float* o, const float* proj, long long ld, const float* decay, const float* u, const float* au,
+                     const pieh_gdelta* d, const pieh_batch* b, void* stream);
+
+/* ---- selective state space layer in its scalar-decay ("state-space duality") form --------------------------------------------
+ * proj fp32 [T, ld]: the convolved channels [x (H P) | B (G N) | C (G N)] start at xbc_off, the H step-size logits at dt_off.
+ *   channels <- silu(causal conv over time + conv_b)         history of taps - 1 rows per sequence slot, zeros before the start
+ *   dt = softplus(dt_logit + dt_bias),  decay = exp(-exp(A_log) dt)              per head
+ *   S_t = decay S_(t-1) + dt B_t x_t^T   (S [N, P], head h reads group h / (H / G));   y_t = S_t^T C_t + D x_t */
+typedef struct pieh_ssd {
+  int H, P, N, G, taps;
+  long long xbc_off, dt_off;
+  const float* conv_w;   /* [H P + 2 G N, taps]; the last tap multiplies the current token */
+  const float* conv_b;   /* [H P + 2 G N] or NULL */
+  const float* dt_bias;  /* [H] */
+  const float* A_log;    /* [H] */
+  const float* D;        /* [H] */
+  float* conv_state;     /* [slots, taps - 1, H P + 2 G N] fp32, oldest first (unused when taps == 1) */
+  float* state;          /* [slots, H, N, P] fp32 */
+} pieh_ssd;
+/* xbc fp32 [T, H P + 2 G N] after convolution and silu; dtd fp32 [T, H, 2] = (dt, decay); then the histories move on. */
+int pieh_ssd_prepare(float* xbc, float* dtd, const float* proj, long long ld, const pieh_ssd* s, const pieh_batch* b,
+                     void* stream);
+/* y fp32 [T, H P]. */
+int pieh_ssd_scan(float* y, const float* xbc, const float* dtd, const pieh_ssd* s, const pieh_batch* b, void* stream);
 
 #ifdef __cplusplus
 }

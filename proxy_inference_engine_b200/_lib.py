@@ -168,7 +168,7 @@ class HybBiasAttn(C.Structure):
                 ("v_pages", C.c_void_p), ("kv_dtype", C.c_int),
                 # optional pieces, zero / NULL = off
                 ("sinks", C.c_void_p), ("gate_heads", C.c_int), ("rot_dims", C.c_int), ("rot_cs", C.c_void_p),
-                ("v_mix", C.c_void_p), ("v_keep", C.c_void_p)]
+                ("v_mix", C.c_void_p), ("v_keep", C.c_void_p), ("sigmoid", C.c_int), ("score_bias", C.c_void_p)]
 
 
 class HybMixSum(C.Structure):
@@ -190,9 +190,24 @@ class HybCanon(C.Structure):
                 ("state", C.c_void_p)]
 
 
+class HybGdelta(C.Structure):
+    """pieh_gdelta"""
+    _fields_ = [("H", C.c_int), ("dk", C.c_int), ("dv", C.c_int), ("r_off", C.c_longlong), ("k_off", C.c_longlong),
+                ("v_off", C.c_longlong), ("a_off", C.c_longlong), ("a_bias", C.c_void_p), ("decay_scale", C.c_float),
+                ("key_eps", C.c_float), ("state", C.c_void_p)]
+
+
+class HybSsd(C.Structure):
+    """pieh_ssd"""
+    _fields_ = [("H", C.c_int), ("P", C.c_int), ("N", C.c_int), ("G", C.c_int), ("taps", C.c_int), ("xbc_off", C.c_longlong),
+                ("dt_off", C.c_longlong), ("conv_w", C.c_void_p), ("conv_b", C.c_void_p), ("dt_bias", C.c_void_p),
+                ("A_log", C.c_void_p), ("D", C.c_void_p), ("conv_state", C.c_void_p), ("state", C.c_void_p)]
+
+
 _PB, _PD, _PA = C.POINTER(HybBatch), C.POINTER(HybDelta), C.POINTER(HybAttn)
 _PBA, _PMS, _PMP = C.POINTER(HybBiasAttn), C.POINTER(HybMixSum), C.POINTER(HybMoePlan)
 _PCN = C.POINTER(HybCanon)
+_PGD, _PSS = C.POINTER(HybGdelta), C.POINTER(HybSsd)
 # libpie_b200_hybrid.so: every symbol include/pie_b200_hybrid.h declares (tests check this), + the page allocator
 HYBRID_SIGNATURES = {
     "pieh_abi_version": (_i, []),
@@ -221,11 +236,18 @@ HYBRID_SIGNATURES = {
     "pieh_canon_conv": (_i, [_PCN, _i, _vp, _i, _PB, _vp]),
     "pieh_mingru_scan": (_i, [_vp, _i, _vp, _ll, _i, _vp, _vp, _PB, _vp]),
     "pieh_latent_prepare": (_i, [_vp, _i, _vp, _ll, _i, _ll, _i, _vp, _vp, _f, _vp, _i, _PB, _vp]),
+    "pieh_linear_act": (_i, [_vp, _i, _ll, _vp, _i, _ll, _vp, _i, _vp, _i, _i, _i, _i, _f, _f, _vp]),
+    "pieh_sandwich_add": (_i, [_vp, _vp, _PMS, _vp, _f, _vp, _vp, _vp, _i, _vp, _f, _i, _i, _vp]),
+    "pieh_gated_group_norm": (_i, [_vp, _i, _vp, _ll, _vp, _ll, _vp, _i, _i, _f, _i, _i, _i, _vp]),
+    "pieh_gdelta_prepare": (_i, [_vp, _vp, _vp, _vp, _ll, _vp, _ll, _PGD, _i, _vp]),
+    "pieh_gdelta_scan": (_i, [_vp, _vp, _ll, _vp, _vp, _vp, _PGD, _PB, _vp]),
+    "pieh_ssd_prepare": (_i, [_vp, _vp, _vp, _ll, _PSS, _PB, _vp]),
+    "pieh_ssd_scan": (_i, [_vp, _vp, _vp, _PSS, _PB, _vp]),
     "pieh_moe_route": (_i, [_vp, _ll, _PMP, _i, _vp]),
     "pieh_moe_linear": (_i, [_vp, _i, _ll, _vp, _i, _ll, _vp, _i, _ll, _i, _i, _i, _i, _i, _f, _f, _f, _PMP, _vp]),
 }
 HYBRID_LIB_PATH = os.environ.get("PIE_HYBRID_LIB") or os.path.join(_HERE, "libpie_b200_hybrid.so")
-EPI_NONE, EPI_RELU2, EPI_SOFTCAP, EPI_STREAMS, EPI_GLU, EPI_SIGMUL = 0, 1, 2, 3, 4, 5
+EPI_NONE, EPI_RELU2, EPI_SOFTCAP, EPI_STREAMS, EPI_GLU, EPI_SIGMUL, EPI_TANH, EPI_XIELU = 0, 1, 2, 3, 4, 5, 6, 7
 
 _lib = None
 _hyb = None

@@ -252,9 +252,15 @@ def _load_maginex(config: dict, path: str, device, dtype):
     return MaginexModel(MaginexArgs.from_dict(config), read_weights(path), device, dtype or "bfloat16")
 
 
+def _load_zelinex(config: dict, path: str, device, dtype):
+    from .zelinex import ZelinexArgs, ZelinexModel
+    return ZelinexModel(ZelinexArgs.from_dict(config), read_weights(path), device, dtype or "bfloat16")
+
+
 # model registry: config.json's "architecture" (or, for Hugging Face / MLX checkpoints, "model_type") -> loader.
 # The reference resolves model_type to a module of PIE/models/ the same way (PIE/models/utils.py:25-48).
-MODEL_REGISTRY = {"llama": _load_llama, "Golitar": _load_golitar, "Babodra": _load_babodra, "Maginex": _load_maginex}
+MODEL_REGISTRY = {"llama": _load_llama, "Golitar": _load_golitar, "Babodra": _load_babodra, "Maginex": _load_maginex,
+                  "Zelinex": _load_zelinex}
 
 
 def model_kind(config: dict) -> str:

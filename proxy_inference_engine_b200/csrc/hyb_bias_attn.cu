@@ -116,11 +116,14 @@ __global__ void __launch_bounds__(kRunWarps * 32) bias_run_kernel(OT* out, const
   const int chunk = ((p - lo + cs) / cs + 31) / 32 * 32;
   const int my_lo = lo + rank * chunk, my_hi = min(p, my_lo + chunk - 1);
   const float slope = a.slopes ? a.slopes[h] : 0.f;
+  // sigmoid weights: no maximum, no denominator -- every partial result is a plain sum (m stays 0, so every merge factor is 1)
+  const bool sgm = a.sigmoid != 0;
+  const float sbias = sgm && a.score_bias ? a.score_bias[h] : 0.f;
   const int32_t* table = b.block_table + (size_t)i * b.bt_stride;
   const KT* kpool = reinterpret_cast<const KT*>(a.k_pages);
   const KT* vpool = reinterpret_cast<const KT*>(a.v_pages);
   const bool vec = (d & 7) == 0;
-  float m = -1e30f, l = 0.f, acc[NV];
+  float m = sgm ? 0.f : -1e30f, l = 0.f, acc[NV];
 #pragma unroll
   for (int x = 0; x < NV; ++x) acc[x] = 0.f;
   for (int base = my_lo + warp * 32; base <= my_hi; base += NW * 32) {
@@ -145,13 +148,18 @@ __global__ void __launch_bounds__(kRunWarps * 32) bias_run_kernel(OT* out, const
       }
       s = dot * a.scale - slope * (float)(p - j);
     }
-    const float n = fmaxf(m, warp_max(s));
-    const float cf = expf(m - n);
-    const float pj = ok ? expf(s - n) : 0.f;
-    l = l * cf + warp_sum(pj);
-    m = n;
+    float pj;
+    if (sgm) {
+      pj = ok ? 1.f / (1.f + expf(-(s + sbias))) : 0.f;
+    } else {
+      const float n = fmaxf(m, warp_max(s));
+      const float cf = expf(m - n);
+      pj = ok ? expf(s - n) : 0.f;
+      l = l * cf + warp_sum(pj);
+      m = n;
 #pragma unroll
-    for (int x = 0; x < NV; ++x) acc[x] *= cf;
+      for (int x = 0; x < NV; ++x) acc[x] *= cf;
+    }
 #pragma unroll 1
     for (int k0 = 0; k0 < 32; k0 += 4) {
       if (base + k0 > my_hi) break;
@@ -182,7 +190,7 @@ __global__ void __launch_bounds__(kRunWarps * 32) bias_run_kernel(OT* out, const
   if (lane == 0) { mine[dv] = m; mine[dv + 1] = l; }
   __syncthreads();
   {                            // the warps of this CTA -> one partial softmax
-    float M = -1e30f, f[NW], L = 0.f;
+    float M = sgm ? 0.f : -1e30f, f[NW], L = 0.f;
 #pragma unroll
     for (int w = 0; w < NW; ++w) M = fmaxf(M, mg[(size_t)w * (dv + 2) + dv]);
 #pragma unroll
@@ -201,9 +209,9 @@ __global__ void __launch_bounds__(kRunWarps * 32) bias_run_kernel(OT* out, const
   if (CLUSTER) cg::this_cluster().sync(); else __syncthreads();
   if (rank == 0) {   // the CTAs of the cluster and the sink -> the output
     // the sink is one more partial softmax: maximum = its logit (0 for the fixed sink), sum 1, no values
-    const bool has_sink = a.sinks != nullptr || a.sink != 0;
+    const bool has_sink = !sgm && (a.sinks != nullptr || a.sink != 0);
     const float sk = a.sinks ? a.sinks[h] : 0.f;
-    float M = has_sink ? sk : -1e30f;
+    float M = sgm ? 0.f : has_sink ? sk : -1e30f;
     float L = 0.f;
     const float* gate = a.g_off >= 0 ? proj + (size_t)t * ld + a.g_off + (a.gate_heads ? (size_t)h : (size_t)h * dv) : nullptr;
     if (CLUSTER) {
@@ -220,7 +228,7 @@ __global__ void __launch_bounds__(kRunWarps * 32) bias_run_kernel(OT* out, const
           const float* src = cl.map_shared_rank(part, r);
           A = fmaf(src[c], expf(src[dv] - M), A);
         }
-        float o = A / L;
+        float o = sgm ? A : A / L;
         if (gate) o *= 1.f / (1.f + expf(-gate[a.gate_heads ? 0 : c]));
         elem<OT>::store(out + ((size_t)t * a.H + h) * dv + c, o);
       }
@@ -230,7 +238,7 @@ __global__ void __launch_bounds__(kRunWarps * 32) bias_run_kernel(OT* out, const
       L = part[dv + 1] * f;
       if (has_sink) L += expf(sk - M);
       for (int c = threadIdx.x; c < dv; c += NTH) {
-        float o = part[c] * f / L;
+        float o = sgm ? part[c] : part[c] * f / L;
         if (gate) o *= 1.f / (1.f + expf(-gate[a.gate_heads ? 0 : c]));
         elem<OT>::store(out + ((size_t)t * a.H + h) * dv + c, o);
       }
@@ -326,7 +334,9 @@ __global__ void __launch_bounds__(128) bias_tile_kernel(__nv_bfloat16* out, cons
 #pragma unroll
   for (int x = 0; x < DT; ++x) o[x][0] = o[x][1] = o[x][2] = o[x][3] = 0.f;
   constexpr float kLog2e = 1.4426950408889634f;
-  const bool has_sink = a.sinks != nullptr || a.sink != 0;
+  const bool sgm = a.sigmoid != 0;                          // sigmoid weights: no running maximum, no denominator
+  const float sb2 = sgm && a.score_bias ? a.score_bias[h] * kLog2e : 0.f;
+  const bool has_sink = !sgm && (a.sinks != nullptr || a.sink != 0);
   const float sk2 = a.sinks ? a.sinks[h] * kLog2e : 0.f;   // the sink's logit in the exp2 domain
   const float m_init = has_sink ? sk2 : -INFINITY;
   float mrun[2] = {m_init, m_init}, lrun[2] = {0.f, 0.f};
@@ -366,6 +376,14 @@ __global__ void __launch_bounds__(128) bias_tile_kernel(__nv_bfloat16* out, cons
       mx0 = fmaxf(mx0, fmaxf(s[n][0], s[n][1]));
       mx1 = fmaxf(mx1, fmaxf(s[n][2], s[n][3]));
     }
+    uint32_t pf[NT][2];
+    if (sgm) {
+#pragma unroll
+      for (int n = 0; n < NT; ++n) {   // a masked score is -inf: exp2(+inf) = inf and the weight is exactly 0
+        pf[n][0] = pack2(1.f / (1.f + exp2f(-(s[n][0] + sb2))), 1.f / (1.f + exp2f(-(s[n][1] + sb2))));
+        pf[n][1] = pack2(1.f / (1.f + exp2f(-(s[n][2] + sb2))), 1.f / (1.f + exp2f(-(s[n][3] + sb2))));
+      }
+    } else {
     mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1)); mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
     mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1)); mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
     if (mx0 > mrun[0]) {
@@ -384,7 +402,6 @@ __global__ void __launch_bounds__(128) bias_tile_kernel(__nv_bfloat16* out, cons
     }
     const float ms0 = mrun[0] == -INFINITY ? 0.f : mrun[0], ms1 = mrun[1] == -INFINITY ? 0.f : mrun[1];
     float ps0 = 0.f, ps1 = 0.f;
-    uint32_t pf[NT][2];
 #pragma unroll
     for (int n = 0; n < NT; ++n) {
       const float e0 = exp2f(s[n][0] - ms0), e1 = exp2f(s[n][1] - ms0);
@@ -394,6 +411,7 @@ __global__ void __launch_bounds__(128) bias_tile_kernel(__nv_bfloat16* out, cons
       pf[n][1] = pack2(e2, e3);
     }
     lrun[0] += ps0; lrun[1] += ps1;
+    }
 #pragma unroll
     for (int kk = 0; kk < 4; ++kk) {
       const uint32_t a0 = pf[2 * kk][0], a1 = pf[2 * kk][1], a2 = pf[2 * kk + 1][0], a3 = pf[2 * kk + 1][1];
@@ -413,7 +431,7 @@ __global__ void __launch_bounds__(128) bias_tile_kernel(__nv_bfloat16* out, cons
     float l = lrun[rr];
     l += __shfl_xor_sync(0xffffffffu, l, 1); l += __shfl_xor_sync(0xffffffffu, l, 2);
     if (has_sink) l += exp2f(sk2 - mrun[rr]);   // the sink's logit against the running maximum
-    inv[rr] = 1.f / l;
+    inv[rr] = sgm ? 1.f : 1.f / l;
   }
   const size_t goff = a.g_off + (a.gate_heads ? (size_t)h : (size_t)h * DV);
   const float* g0 = a.g_off >= 0 ? proj + (size_t)(row0 + min(r0, nrows - 1)) * ld + goff : nullptr;
@@ -458,7 +476,7 @@ static bool bias_attn_ok(const pieh_bias_attn* a) {
   return a && a->H > 0 && a->G > 0 && a->H % a->G == 0 && a->d > 0 && a->dv > 0 && a->dv <= 512 && a->d <= 1024 &&
          a->k_pages && a->v_pages && a->temp_every >= 0.0 && a->window >= 0 && a->k_off >= 0 && a->v_off >= 0 &&
          a->rot_dims >= 0 && a->rot_dims <= a->d && (a->rot_dims & 1) == 0 && (a->rot_dims == 0 || a->rot_cs) &&
-         (!a->v_mix || a->v_keep);
+         (!a->v_mix || a->v_keep) && (a->sigmoid == 0 || a->sigmoid == 1);
 }
 
 template <typename KT, typename OT, int NV>

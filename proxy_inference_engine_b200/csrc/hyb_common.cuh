@@ -105,6 +105,10 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
 }
 __device__ __forceinline__ float silu_f(float z) { return z / (1.f + expf(-z)); }
 __device__ __forceinline__ float softplus_f(float z) { return z > 20.f ? z : log1pf(expf(z)); }
+// a z^2 + z / 2 above zero, b (e^z - 1 - z) + z / 2 at and below it (continuous, slope 1/2 at zero from both sides)
+__device__ __forceinline__ float xielu_f(float z, float a, float b) {
+  return z > 0.f ? fmaf(a * z, z, 0.5f * z) : fmaf(b, expm1f(z) - z, 0.5f * z);
+}
 
 // out dtype dispatch for host launchers
 #define PIEH_DISPATCH_DTYPE(code, T, ...)                     \

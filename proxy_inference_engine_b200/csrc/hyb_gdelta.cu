@@ -1,0 +1,192 @@
+// Generalized delta rule over ragged steps: a matrix state S [dk, dv] per (sequence, head) in fp32, carried in a slot.
+//   per token:  p = u^T S;   S <- diag(w) S - (a * u) p + k v^T;   o = S^T r
+// with a decay w per key channel, a removal rate a per key channel and the unit key u = k / sqrt(|k|^2 + eps): the old
+// content is forgotten channel by channel and, on top of that, erased along the direction of the current key.
+// gdelta_prepare_kernel  per (token, head): w = exp(-c sigmoid(decay logits)), a = sigmoid(. + bias), u and a * u
+// gdelta_scan_kernel     the recurrence.  A column of S lives in the registers of R adjacent lanes (RPT rows each), so a
+//                        token costs 4 RPT multiply-adds and two log2(R)-step shuffle chains per thread and no barrier; the
+//                        token's five key-sized vectors and its value entries come through shared memory a chunk of tokens
+//                        at a time, cp.async filling one buffer while the recurrence walks the other
+// Everything here is fp32.
+#include "hyb_common.cuh"
+
+namespace pieh {
+
+// grid (T, H)
+__global__ void __launch_bounds__(128) gdelta_prepare_kernel(float* decay, float* u, float* au, const float* proj,
+                                                             long long ld, const float* dl, long long dl_ld,
+                                                             const pieh_gdelta d) {
+  __shared__ float red[33];
+  pdl_sync();
+  const int t = blockIdx.x, h = blockIdx.y;
+  const int dk = d.dk;
+  const float* kr = proj + (size_t)t * ld + d.k_off + (size_t)h * dk;
+  const float* ar = proj + (size_t)t * ld + d.a_off + (size_t)h * dk;
+  const float* lr = dl + (size_t)t * dl_ld + (size_t)h * dk;
+  float ss = 0.f;
+  for (int c = threadIdx.x; c < dk; c += blockDim.x) ss = fmaf(kr[c], kr[c], ss);
+  const float inv = 1.f / sqrtf(block_sum(ss, red) + d.key_eps);
+  const size_t o = ((size_t)t * d.H + h) * dk;
+  for (int c = threadIdx.x; c < dk; c += blockDim.x) {
+    const float uu = kr[c] * inv;
+    const float a = 1.f / (1.f + expf(-(ar[c] + (d.a_bias ? d.a_bias[(size_t)h * dk + c] : 0.f))));
+    decay[o + c] = expf(-d.decay_scale / (1.f + expf(-lr[c])));
+    u[o + c] = uu;
+    au[o + c] = a * uu;
+  }
+}
+
+constexpr int kGdThreads = 128;
+
+__device__ __forceinline__ void gd_cp_async(float* smem_dst, const float* gsrc, int bytes) {
+  const uint32_t dst = (uint32_t)__cvta_generic_to_shared(smem_dst);
+  if (bytes == 16) asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(gsrc) : "memory");
+  else asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(gsrc) : "memory");
+}
+
+// grid (ceil(dv / cols), H, sequences); chunk: tokens per shared-memory buffer
+template <int RPT>
+__global__ void __launch_bounds__(kGdThreads) gdelta_scan_kernel(float* o, const float* proj, long long ld,
+                                                                 const float* decay, const float* u, const float* au,
+                                                                 const pieh_gdelta d, const pieh_batch b, int R, int chunk) {
+  extern __shared__ __align__(16) float sm[];
+  pdl_sync();
+  const int cols = kGdThreads / R;
+  const int h = blockIdx.y, i = blockIdx.z;
+  const int start = b.seq_start[i], n = b.seq_len[i], ctx = b.seq_ctx[i];
+  const int rl = threadIdx.x % R, cl = threadIdx.x / R;
+  const int j = blockIdx.x * cols + cl;           // column of S (feature of v)
+  const bool col_ok = j < d.dv;
+  const int dk = d.dk, dv = d.dv;
+  // one buffer: per token [w | u | a u | k | r] (dk each), then the chunk's value entries [chunk, cols]
+  const int tok_floats = 5 * dk;
+  const int buf_floats = chunk * (tok_floats + cols);
+  float* S_g = d.state + (((size_t)b.seq_slot[i] * d.H + h) * dk) * dv;
+  float S[RPT];
+#pragma unroll
+  for (int r = 0; r < RPT; ++r) {
+    const int row = r * R + rl;   // rows are dealt round-robin to the R lanes: neighbouring lanes read neighbouring banks
+    S[r] = (ctx > 0 && col_ok && row < dk) ? S_g[(size_t)row * dv + j] : 0.f;
+  }
+  // 16-byte copies need every source 16-byte aligned: whole multiples of 4 floats everywhere a row starts
+  const bool vec = (dk & 3) == 0 && (ld & 3) == 0 && (d.k_off & 3) == 0 && (d.r_off & 3) == 0 &&
+                   (reinterpret_cast<uintptr_t>(proj) & 15) == 0 && (reinterpret_cast<uintptr_t>(decay) & 15) == 0 &&
+                   (reinterpret_cast<uintptr_t>(u) & 15) == 0 && (reinterpret_cast<uintptr_t>(au) & 15) == 0;
+  auto fill = [&](int which, int c0) {
+    float* base = sm + which * buf_floats;
+    float* vs = base + chunk * tok_floats;
+    const int nc = min(chunk, n - c0);
+    const int step = vec ? 4 : 1, per = dk / step;
+    for (int e = threadIdx.x; e < nc * per; e += kGdThreads) {
+      const int tt = e / per, r = (e - tt * per) * step;
+      const size_t row = (size_t)(start + c0 + tt);
+      const size_t s3 = (row * d.H + h) * dk + r;
+      float* dst = base + tt * tok_floats + r;
+      gd_cp_async(dst, decay + s3, 4 * step);
+      gd_cp_async(dst + dk, u + s3, 4 * step);
+      gd_cp_async(dst + 2 * dk, au + s3, 4 * step);
+      gd_cp_async(dst + 3 * dk, proj + row * ld + d.k_off + (size_t)h * dk + r, 4 * step);
+      gd_cp_async(dst + 4 * dk, proj + row * ld + d.r_off + (size_t)h * dk + r, 4 * step);
+    }
+    for (int e = threadIdx.x; e < nc * cols; e += kGdThreads) {
+      const int tt = e / cols, c = e - tt * cols;
+      const int jj = min(blockIdx.x * cols + c, dv - 1);
+      gd_cp_async(vs + e, proj + (size_t)(start + c0 + tt) * ld + d.v_off + (size_t)h * dv + jj, 4);
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  float out_prev = 0.f;   // this lane's share of the last token's read-out, not yet summed over the R lanes
+  int row_prev = -1;
+  fill(0, 0);
+  for (int c0 = 0, which = 0; c0 < n; c0 += chunk, which ^= 1) {
+    const int nc = min(chunk, n - c0);
+    if (c0 + chunk < n) {
+      fill(which ^ 1, c0 + chunk);
+      asm volatile("cp.async.wait_group 1;" ::: "memory");
+    } else {
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
+    }
+    __syncthreads();
+    const float* base = sm + which * buf_floats;
+    const float* vs = base + chunk * tok_floats;
+    for (int tt = 0; tt < nc; ++tt) {
+      const float* tk = base + tt * tok_floats + rl;
+      float pp[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int r = 0; r < RPT; ++r)
+        if (r * R + rl < dk) pp[r & 3] = fmaf(S[r], tk[dk + r * R], pp[r & 3]);
+      float p = (pp[0] + pp[1]) + (pp[2] + pp[3]);
+      // the read-out of the PREVIOUS token is reduced over the R lanes together with this token's projection: two
+      // independent shuffle chains instead of two in a row on the recurrence's critical path
+      for (int off = 1; off < R; off <<= 1) {
+        p += __shfl_xor_sync(0xffffffffu, p, off);
+        out_prev += __shfl_xor_sync(0xffffffffu, out_prev, off);
+      }
+      if (row_prev >= 0 && rl == 0 && col_ok) o[((size_t)row_prev * d.H + h) * dv + j] = out_prev;
+      const float vj = vs[tt * cols + cl];
+      float oo[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int r = 0; r < RPT; ++r) {
+        if (r * R + rl < dk) {
+          const float* e = tk + r * R;
+          S[r] = fmaf(e[0], S[r], fmaf(e[3 * dk], vj, -e[2 * dk] * p));
+          oo[r & 3] = fmaf(S[r], e[4 * dk], oo[r & 3]);
+        }
+      }
+      out_prev = (oo[0] + oo[1]) + (oo[2] + oo[3]);
+      row_prev = start + c0 + tt;
+    }
+    __syncthreads();   // everyone is done with this buffer before the next fill overwrites it
+  }
+  for (int off = 1; off < R; off <<= 1) out_prev += __shfl_xor_sync(0xffffffffu, out_prev, off);
+  if (row_prev >= 0 && rl == 0 && col_ok) o[((size_t)row_prev * d.H + h) * dv + j] = out_prev;
+  if (col_ok) {
+#pragma unroll
+    for (int r = 0; r < RPT; ++r) {
+      const int row = r * R + rl;
+      if (row < dk) S_g[(size_t)row * dv + j] = S[r];
+    }
+  }
+}
+
+static bool gdelta_ok(const pieh_gdelta* d) {
+  return d && d->H > 0 && d->dk > 0 && d->dv > 0 && d->dk <= 512 && d->dv <= 65535 && d->r_off >= 0 && d->k_off >= 0 &&
+         d->v_off >= 0 && d->a_off >= 0 && d->state && d->key_eps >= 0.f;
+}
+
+}  // namespace pieh
+
+using namespace pieh;
+
+extern "C" int pieh_gdelta_prepare(float* decay, float* u, float* au, const float* proj, long long ld,
+                                   const float* decay_logits, long long dl_ld, const pieh_gdelta* d, int T, void* stream) {
+  if (!decay || !u || !au || !proj || !decay_logits || !d) return PIE_ENULL;
+  if (!gdelta_ok(d) || T < 0 || d->H > 65535) return PIE_EINVAL_SHAPE;
+  if (T == 0) return PIE_OK;
+  count_launch();
+  return status_of(launch_k(gdelta_prepare_kernel, dim3(T, d->H), dim3(128), 0, (cudaStream_t)stream, decay, u, au, proj, ld,
+                            decay_logits, dl_ld, *d));
+}
+
+extern "C" int pieh_gdelta_scan(float* o, const float* proj, long long ld, const float* decay, const float* u,
+                                const float* au, const pieh_gdelta* d, const pieh_batch* b, void* stream) {
+  if (!o || !proj || !decay || !u || !au || !d || !b) return PIE_ENULL;
+  if (!gdelta_ok(d) || d->H > 65535 || b->n_seq > 65535) return PIE_EINVAL_SHAPE;
+  if (b->T == 0) return PIE_OK;
+  constexpr int RPT = 16;            // rows of a state column per lane
+  int R = 1;
+  while (R * RPT < d->dk) R <<= 1;   // lanes per column, a power of two <= 32
+  const int cols = kGdThreads / R;
+  // tokens per buffer: 16 where two buffers fit the shared memory a CTA may have, fewer for very wide keys
+  int chunk = 16;
+  while (chunk > 1 && (size_t)2 * chunk * (5 * d->dk + cols) * 4 > 160 * 1024) chunk >>= 1;
+  const size_t smem = (size_t)2 * chunk * (5 * d->dk + cols) * 4;
+  static bool opted = false;
+  if (smem > 48 * 1024 && !opted) {
+    cudaFuncSetAttribute(gdelta_scan_kernel<RPT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    opted = true;
+  }
+  count_launch();
+  return status_of(launch_k(gdelta_scan_kernel<RPT>, dim3((d->dv + cols - 1) / cols, d->H, b->n_seq), dim3(kGdThreads), smem,
+                            (cudaStream_t)stream, o, proj, ld, decay, u, au, *d, *b, R, chunk));
+}

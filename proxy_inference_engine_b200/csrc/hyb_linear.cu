@@ -21,6 +21,8 @@ __device__ __forceinline__ void lin_store(const LinArgs& a, int m, int n, float 
   if (a.bias) y += a.bias[n];
   if (a.epi == PIEH_EPI_RELU2) { y = fmaxf(y, 0.f); y = y * y; }
   else if (a.epi == PIEH_EPI_SOFTCAP) y = a.epi_a * tanhf(y / a.epi_a);
+  else if (a.epi == PIEH_EPI_TANH) y = tanhf(y);
+  else if (a.epi == PIEH_EPI_XIELU) y = xielu_f(y, a.epi_a, a.epi_b);
   else if (a.epi == PIEH_EPI_SIGMUL) y *= 1.f / (1.f + expf(-a.gate[(size_t)blockIdx.z * a.gate_bs + (size_t)m * a.gate_ld + n]));
   if (a.epi == PIEH_EPI_STREAMS) {
     float* xs = reinterpret_cast<float*>(a.out) + (size_t)m * a.S * a.N + n;
@@ -293,6 +295,18 @@ extern "C" int pieh_linear(void* out, int out_dtype, long long out_ld, const voi
   LinArgs a{out, out_ld, x, x_ld, w, bias, M, N, K, epilogue, epi_a, mix, outw, S};
   cudaStream_t st = (cudaStream_t)stream;
   return run_linear(a, out_dtype, x_dtype, w_dtype, st);
+}
+
+extern "C" int pieh_linear_act(void* out, int out_dtype, long long out_ld, const void* x, int x_dtype, long long x_ld,
+                               const void* w, int w_dtype, const float* bias, int M, int N, int K, int act, float act_a,
+                               float act_b, void* stream) {
+  if (!out || !x || !w) return PIE_ENULL;
+  if (M < 0 || N <= 0 || K <= 0) return PIE_EINVAL_SHAPE;
+  if (M == 0) return PIE_OK;
+  if (act != PIEH_EPI_NONE && act != PIEH_EPI_RELU2 && act != PIEH_EPI_TANH && act != PIEH_EPI_XIELU) return PIE_EUNSUPPORTED;
+  LinArgs a{out, out_ld, x, x_ld, w, bias, M, N, K, act, act_a, nullptr, nullptr, 0};
+  a.epi_b = act_b;
+  return run_linear(a, out_dtype, x_dtype, w_dtype, (cudaStream_t)stream);
 }
 
 namespace pieh {

@@ -118,6 +118,8 @@ __device__ __forceinline__ void umma_store(const LinArgs& a, int m, int n0, cons
       if (a.bias && n < a.N) t += a.bias[n];
       if (a.epi == PIEH_EPI_RELU2) { t = fmaxf(t, 0.f); t = t * t; }
       else if (a.epi == PIEH_EPI_SOFTCAP) t = a.epi_a * tanhf(t / a.epi_a);
+      else if (a.epi == PIEH_EPI_TANH) t = tanhf(t);
+      else if (a.epi == PIEH_EPI_XIELU) t = xielu_f(t, a.epi_a, a.epi_b);
       else if (a.epi == PIEH_EPI_SIGMUL && n < a.N) t *= 1.f / (1.f + __expf(-gate[n]));
       y[q] = t;
     }

@@ -1,5 +1,5 @@
 """Continuous-batching engine for models that step over ``ragged.BatchDetails`` with a ``cache.HybridCache``
-(``golitar.GolitarModel``, ``babodra.BabodraModel``, ``maginex.MaginexModel``): the generate loop of PIE (PIE/engine/inference_engine.py:228-297) lifted from one sequence to
+(``golitar.GolitarModel``, ``babodra.BabodraModel``, ``maginex.MaginexModel``, ``zelinex.ZelinexModel``): the generate loop of PIE (PIE/engine/inference_engine.py:228-297) lifted from one sequence to
 a changing set of them.
 
     eng = HybridEngine(model, max_tokens=4096, max_seqs=4)
