@@ -64,9 +64,12 @@ def attention_branch(h, w, p, m):
     q = (h @ w[p + "q"].T).view(L, H, d)
     k = (h @ w[p + "k"].T).view(L, G, d)
     v = (h @ w[p + "v"].T).view(L, G, dv)
-    pos = torch.arange(L)
-    q, k = rotate_half(q, pos, m["rot"]["dims"], m["rot"]["base"]), rotate_half(k, pos, m["rot"]["dims"], m["rot"]["base"])
-    o = sigmoid_window_attention(q, k, v, m["scale"], m["mask"]["size"], w[p + "pb"])
+    rot = m.get("rot")
+    if rot and rot["dims"]:
+        pos = torch.arange(L)
+        q, k = rotate_half(q, pos, rot["dims"], rot["base"]), rotate_half(k, pos, rot["dims"], rot["base"])
+    window = (m.get("mask") or {}).get("size") or L          # no mask: every earlier token
+    o = sigmoid_window_attention(q, k, v, m["scale"], window, w[p + "pb"])
     return o.reshape(L, H * dv) @ w[p + "o"].T
 
 
@@ -219,3 +222,36 @@ def forward(cfg, weights, tokens, trace=None, margins=None):
         if trace is not None:
             trace.append(x.clone())
     return (unit_rms(x, eps) * w["final.norm"]) @ w["embed"].T
+
+
+def random_config(vocab=96, width=64, pattern="gp", ffs="dm", heads=4, kv_heads=2, dim=16, vdim=24, window=6, rot_dims=8,
+                  rot_base=10000.0, scale=None, s_heads=4, s_vdim=8, state=12, groups=2, conv=3, norm_groups=2, d_heads=2,
+                  d_dim=16, ff=48, experts=6, top=2, expert_ff=24, shared_ff=16, router_scale=1.5, left_scale=1.1,
+                  right_scale=0.8, mult=0.7, eps=1e-5, loop=(0, 1, 2)):
+    """A small configuration: pattern 'g' = general_delta, 'p' = parallel; ffs per layer 'd' dense, 'm' experts, '-' none
+    (the last letter repeats); loop (start, stop, times) or None."""
+    layers = []
+    for i, c in enumerate(pattern):
+        if c == "g":
+            mixer = {"heads": d_heads, "dim": d_dim}
+        else:
+            left = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim,
+                    "scale": scale if scale is not None else dim ** -0.5, "mask": {"size": window}}
+            if rot_dims:
+                left["rot"] = {"base": rot_base, "dims": rot_dims}
+            mixer = {"left": left, "left_scale": left_scale, "right_scale": right_scale,
+                     "right": {"heads": s_heads, "vdim": s_vdim, "state": state, "groups": groups, "conv": conv,
+                               "norm_groups": norm_groups}}
+        f = ffs[min(i, len(ffs) - 1)]
+        mlp = None
+        if f == "d":
+            mlp = {"kind": "dense", "ff": ff}
+        elif f == "m":
+            mlp = {"kind": "moe", "expert": {"ff": expert_ff}, "router": {"experts": experts, "top": top, "scale": router_scale},
+                   "shared": {"ff": shared_ff} if shared_ff else None}
+        layers.append({"type": "general_delta" if c == "g" else "parallel", "mixer": mixer, "mlp": mlp})
+    cfg = {"architecture": "Zelinex", "vocab": vocab, "width": width, "norm": {"eps": eps}, "residual_mult": mult,
+           "layers": layers}
+    if loop:
+        cfg["loop"] = {"start": loop[0], "stop": min(loop[1], len(layers)), "times": loop[2]}
+    return cfg
