@@ -38,11 +38,12 @@ def parse():
     ap.add_argument("--no-70b", action="store_true", help="N > 1: skip the Llama-3.1-70B tensor-parallel sub-records")
     ap.add_argument("--no-config3", action="store_true", help="skip the 8-bit / batch-32 / paged-KV sub-record (BASELINE configs[2])")
     ap.add_argument("--no-prefill", action="store_true", help="skip the prefill GEMM figure (BASELINE config 4 shapes)")
-    ap.add_argument("--family", default="llama", choices=("llama", "golitar", "babodra", "maginex"),
+    ap.add_argument("--family", default="llama", choices=("llama", "golitar", "babodra", "maginex", "zelinex"),
                     help="golitar: prefill / decode throughput and per-operator rooflines of the Golitar family at --size, "
                          "beside the quantized Llama path at equal size; babodra: the same for the Babodra family, beside "
-                         "Golitar at equal size (its own JSON line; the default workload is untouched)")
-    ap.add_argument("--size", default="1b", help="--family golitar | babodra: layer sizes, 1b or 8b")
+                         "Golitar at equal size; maginex: beside Babodra; zelinex: beside Golitar (its own JSON line; the default "
+                         "workload is untouched)")
+    ap.add_argument("--size", default="1b", help="--family golitar | babodra | maginex | zelinex: layer sizes, 1b or 8b")
     return ap.parse_args()
 
 
@@ -681,7 +682,7 @@ def run_golitar(a):
 
 if __name__ == "__main__":
     args = parse()
-    if args.family in ("golitar", "babodra", "maginex"):
+    if args.family in ("golitar", "babodra", "maginex", "zelinex"):
         run_golitar(args)
     elif args.impl == "reference":
         run_reference(args)

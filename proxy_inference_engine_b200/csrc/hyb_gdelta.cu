@@ -8,6 +8,8 @@
 //                        token's five key-sized vectors and its value entries come through shared memory a chunk of tokens
 //                        at a time, cp.async filling one buffer while the recurrence walks the other
 // Everything here is fp32.
+#include <stdlib.h>
+
 #include "hyb_common.cuh"
 
 namespace pieh {
@@ -149,6 +151,132 @@ __global__ void __launch_bounds__(kGdThreads) gdelta_scan_kernel(float* o, const
   }
 }
 
+// The same recurrence with the key size and the lanes per column fixed at compile time (DK = 16 R): a lane owns four runs of
+// four neighbouring state rows, so a token's five key-sized vectors arrive as 20 16-byte shared-memory loads with constant
+// offsets instead of 80 scalar ones with computed addresses, and nothing is predicated.  Needs every row start 16-byte aligned.
+template <int DK, int R>
+__global__ void __launch_bounds__(kGdThreads) gdelta_scan_fixed_kernel(float* o, const float* proj, long long ld,
+                                                                       const float* decay, const float* u, const float* au,
+                                                                       const pieh_gdelta d, const pieh_batch b) {
+  constexpr int RPT = DK / R, Q = RPT / 4, cols = kGdThreads / R, chunk = 16;
+  constexpr int tok_floats = 5 * DK, buf_floats = chunk * (tok_floats + cols);
+  static_assert(RPT % 4 == 0 && R <= 32 && (R & (R - 1)) == 0, "a lane owns whole runs of four rows");
+  extern __shared__ __align__(16) float sm[];
+  pdl_sync();
+  const int h = blockIdx.y, i = blockIdx.z;
+  const int start = b.seq_start[i], n = b.seq_len[i], ctx = b.seq_ctx[i];
+  const int rl = threadIdx.x % R, cl = threadIdx.x / R;
+  const int j = blockIdx.x * cols + cl;           // column of S (feature of v)
+  const int dv = d.dv;
+  const bool col_ok = j < dv;
+  float* S_g = d.state + (((size_t)b.seq_slot[i] * d.H + h) * DK) * dv;
+  float S[RPT];   // S[4 q + e] is state row q * 4 R + 4 rl + e
+#pragma unroll
+  for (int q = 0; q < Q; ++q)
+#pragma unroll
+    for (int e = 0; e < 4; ++e)
+      S[4 * q + e] = (ctx > 0 && col_ok) ? S_g[(size_t)(q * 4 * R + 4 * rl + e) * dv + j] : 0.f;
+  auto fill = [&](int which, int c0) {
+    float* base = sm + which * buf_floats;
+    float* vs = base + chunk * tok_floats;
+    const int nc = min(chunk, n - c0);
+    constexpr int per = DK / 4;
+    for (int e = threadIdx.x; e < nc * per; e += kGdThreads) {
+      const int tt = e / per, r = (e - tt * per) * 4;
+      const size_t row = (size_t)(start + c0 + tt);
+      const size_t s3 = (row * d.H + h) * DK + r;
+      float* dst = base + tt * tok_floats + r;
+      gd_cp_async(dst, decay + s3, 16);
+      gd_cp_async(dst + DK, u + s3, 16);
+      gd_cp_async(dst + 2 * DK, au + s3, 16);
+      gd_cp_async(dst + 3 * DK, proj + row * ld + d.k_off + (size_t)h * DK + r, 16);
+      gd_cp_async(dst + 4 * DK, proj + row * ld + d.r_off + (size_t)h * DK + r, 16);
+    }
+    for (int e = threadIdx.x; e < nc * cols; e += kGdThreads) {
+      const int tt = e / cols, c = e - tt * cols;
+      const int jj = min(blockIdx.x * cols + c, dv - 1);
+      gd_cp_async(vs + e, proj + (size_t)(start + c0 + tt) * ld + d.v_off + (size_t)h * dv + jj, 4);
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  float out_prev = 0.f;
+  int row_prev = -1;
+  fill(0, 0);
+  for (int c0 = 0, which = 0; c0 < n; c0 += chunk, which ^= 1) {
+    const int nc = min(chunk, n - c0);
+    if (c0 + chunk < n) {
+      fill(which ^ 1, c0 + chunk);
+      asm volatile("cp.async.wait_group 1;" ::: "memory");
+    } else {
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
+    }
+    __syncthreads();
+    const float* base = sm + which * buf_floats;
+    const float* vs = base + chunk * tok_floats;
+#pragma unroll 2
+    for (int tt = 0; tt < nc; ++tt) {
+      const float4* t4 = reinterpret_cast<const float4*>(base + tt * tok_floats) + rl;   // + q R: run q; + DK / 4: next vector
+      float4 uu[Q], ww[Q], aa[Q], kk[Q], rr[Q];
+#pragma unroll
+      for (int q = 0; q < Q; ++q) {
+        ww[q] = t4[q * R]; uu[q] = t4[DK / 4 + q * R]; aa[q] = t4[2 * (DK / 4) + q * R];
+        kk[q] = t4[3 * (DK / 4) + q * R]; rr[q] = t4[4 * (DK / 4) + q * R];
+      }
+      float pp[Q];
+#pragma unroll
+      for (int q = 0; q < Q; ++q)
+        pp[q] = fmaf(S[4 * q + 3], uu[q].w, fmaf(S[4 * q + 2], uu[q].z, fmaf(S[4 * q + 1], uu[q].y, S[4 * q] * uu[q].x)));
+      float p = pp[0];
+#pragma unroll
+      for (int q = 1; q < Q; ++q) p += pp[q];
+#pragma unroll
+      for (int off = 1; off < R; off <<= 1) {
+        p += __shfl_xor_sync(0xffffffffu, p, off);
+        out_prev += __shfl_xor_sync(0xffffffffu, out_prev, off);
+      }
+      if (row_prev >= 0 && rl == 0 && col_ok) o[((size_t)row_prev * d.H + h) * dv + j] = out_prev;
+      const float vj = vs[tt * cols + cl];
+      float oo[Q];
+#pragma unroll
+      for (int q = 0; q < Q; ++q) {
+        S[4 * q] = fmaf(ww[q].x, S[4 * q], fmaf(kk[q].x, vj, -aa[q].x * p));
+        S[4 * q + 1] = fmaf(ww[q].y, S[4 * q + 1], fmaf(kk[q].y, vj, -aa[q].y * p));
+        S[4 * q + 2] = fmaf(ww[q].z, S[4 * q + 2], fmaf(kk[q].z, vj, -aa[q].z * p));
+        S[4 * q + 3] = fmaf(ww[q].w, S[4 * q + 3], fmaf(kk[q].w, vj, -aa[q].w * p));
+        oo[q] = fmaf(S[4 * q + 3], rr[q].w, fmaf(S[4 * q + 2], rr[q].z, fmaf(S[4 * q + 1], rr[q].y, S[4 * q] * rr[q].x)));
+      }
+      out_prev = oo[0];
+#pragma unroll
+      for (int q = 1; q < Q; ++q) out_prev += oo[q];
+      row_prev = start + c0 + tt;
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int off = 1; off < R; off <<= 1) out_prev += __shfl_xor_sync(0xffffffffu, out_prev, off);
+  if (row_prev >= 0 && rl == 0 && col_ok) o[((size_t)row_prev * d.H + h) * dv + j] = out_prev;
+  if (col_ok) {
+#pragma unroll
+    for (int q = 0; q < Q; ++q)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) S_g[(size_t)(q * 4 * R + 4 * rl + e) * dv + j] = S[4 * q + e];
+  }
+}
+
+template <int DK, int R>
+static cudaError_t launch_gdelta_fixed(float* o, const float* proj, long long ld, const float* decay, const float* u,
+                                       const float* au, const pieh_gdelta& d, const pieh_batch& b, cudaStream_t st) {
+  constexpr int cols = kGdThreads / R;
+  constexpr size_t smem = (size_t)2 * 16 * (5 * DK + cols) * 4;
+  static bool opted = false;
+  if (smem > 48 * 1024 && !opted) {
+    cudaFuncSetAttribute(gdelta_scan_fixed_kernel<DK, R>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    opted = true;
+  }
+  return launch_k(gdelta_scan_fixed_kernel<DK, R>, dim3((d.dv + cols - 1) / cols, d.H, b.n_seq), dim3(kGdThreads), smem, st, o,
+                  proj, ld, decay, u, au, d, b);
+}
+
 static bool gdelta_ok(const pieh_gdelta* d) {
   return d && d->H > 0 && d->dk > 0 && d->dv > 0 && d->dk <= 512 && d->dv <= 65535 && d->r_off >= 0 && d->k_off >= 0 &&
          d->v_off >= 0 && d->a_off >= 0 && d->state && d->key_eps >= 0.f;
@@ -173,6 +301,17 @@ extern "C" int pieh_gdelta_scan(float* o, const float* proj, long long ld, const
   if (!o || !proj || !decay || !u || !au || !d || !b) return PIE_ENULL;
   if (!gdelta_ok(d) || d->H > 65535 || b->n_seq > 65535) return PIE_EINVAL_SHAPE;
   if (b->T == 0) return PIE_OK;
+  const bool aligned = (ld & 3) == 0 && (d->k_off & 3) == 0 && (d->r_off & 3) == 0 &&
+                       ((reinterpret_cast<uintptr_t>(proj) | reinterpret_cast<uintptr_t>(decay) |
+                         reinterpret_cast<uintptr_t>(u) | reinterpret_cast<uintptr_t>(au)) & 15) == 0;
+  static const bool generic_only = [] { const char* e = getenv("PIE_HYBRID_NO_FIXED_SCAN"); return e && e[0] == '1'; }();
+  if (aligned && !generic_only && (d->dk == 32 || d->dk == 64 || d->dk == 128)) {
+    count_launch();
+    cudaStream_t st = (cudaStream_t)stream;
+    return status_of(d->dk == 32 ? launch_gdelta_fixed<32, 2>(o, proj, ld, decay, u, au, *d, *b, st)
+                     : d->dk == 64 ? launch_gdelta_fixed<64, 4>(o, proj, ld, decay, u, au, *d, *b, st)
+                                   : launch_gdelta_fixed<128, 8>(o, proj, ld, decay, u, au, *d, *b, st));
+  }
   constexpr int RPT = 16;            // rows of a state column per lane
   int R = 1;
   while (R * RPT < d->dk) R <<= 1;   // lanes per column, a power of two <= 32

@@ -1,9 +1,9 @@
-"""Throughput of the Golitar, Babodra and Maginex families at layer sizes of real models (random weights), with every
-operator of the step timed in place and set against its roofline.  Golitar is shown beside the quantized Llama path at
-equal width / feed-forward / depth; Babodra beside Golitar, and Maginex beside Babodra, at equal width / depth / active
-feed-forward size.
+"""Throughput of the Golitar, Babodra, Maginex and Zelinex families at layer sizes of real models (random weights), with
+every operator of the step timed in place and set against its roofline.  Golitar is shown beside the quantized Llama path
+at equal width / feed-forward / depth; Babodra beside Golitar, Maginex beside Babodra, and Zelinex beside Golitar (the other
+family built on a matrix-state recurrence and windowed attention), at equal width / depth / active feed-forward size.
 
-``run(size, ...)`` is what ``bench.py --family golitar|babodra|maginex`` prints.  Method: one prompt of ``prompt`` tokens goes through
+``run(size, ...)`` is what ``bench.py --family golitar|babodra|maginex|zelinex`` prints.  Method: one prompt of ``prompt`` tokens goes through
 ``HybridEngine.forward`` in portions of ``portion`` rows (prefill tok/s, CUDA events around all portions), then ``batch``
 sequences decode ``steps`` tokens each (decode tok/s).  The per-operator table wraps every library call of one prefill
 portion and one decode step in a CUDA event pair; bytes and flops are the algorithmic ones of the call's shapes, the
@@ -24,6 +24,9 @@ SIZES = {
                                                      groups=(4, 2), expert_ff=1536, shared_ff=2048),
                mag=dict(pattern="almalmalmalmalma", heads=16, kv_heads=4, dim=128, vdim=128, window=1024, rot_dims=64,
                         q_rank=768, kv_rank=128, gru=4096, experts=16, top=4, expert_ff=1536, shared_ff=2048, taps=4),
+               zel=dict(pattern="gpgpgpgpgpgp", loop=(0, 4, 2), d_heads=16, d_dim=128, heads=16, kv_heads=4, dim=128, vdim=128,
+                        window=1024, rot_dims=64, s_heads=32, s_vdim=64, state=128, groups=2, norm_groups=2, conv=4,
+                        experts=16, top=4, expert_ff=1536, shared_ff=2048),
                llama=dict(hidden_size=2048, intermediate_size=8192, num_attention_heads=32,
                                                        num_key_value_heads=8, head_dim=64, vocab_size=32000)),
     "8b": dict(width=4096, ff=14336, vocab=32000, pattern="dddadddA", dH=32, dG=16, dk=128, dv=128, aH=32, aG=8, ad=64,
@@ -31,6 +34,9 @@ SIZES = {
                                               expert_ff=3072, shared_ff=2048),
                mag=dict(pattern="almalmal", heads=32, kv_heads=8, dim=128, vdim=128, window=2048, rot_dims=64, q_rank=1536,
                         kv_rank=128, gru=8192, experts=16, top=4, expert_ff=3072, shared_ff=2048, taps=4),
+               zel=dict(pattern="gpgpgp", loop=(0, 2, 2), d_heads=32, d_dim=128, heads=32, kv_heads=8, dim=128, vdim=128,
+                        window=2048, rot_dims=64, s_heads=64, s_vdim=64, state=128, groups=2, norm_groups=2, conv=4,
+                        experts=16, top=4, expert_ff=3072, shared_ff=2048),
                llama=dict(hidden_size=4096, intermediate_size=14336, num_attention_heads=32,
                                                 num_key_value_heads=8, head_dim=128, vocab_size=32000)),
 }
@@ -88,6 +94,30 @@ def maginex_config(size: str) -> dict:
             "embedding": {"scale": 8.0}, "canon": {"taps": m["taps"]}, "layers": layers}
 
 
+def zelinex_config(size: str) -> dict:
+    """Same width as the others and the same number of layer RUNS (part of the stack is looped twice); generalized-delta
+    layers carry the dense feed-forward of golitar_config, the parallel (windowed sigmoid attention + state-space) layers a
+    mixture with the ACTIVE size of babodra_config's."""
+    s = SIZES[size]
+    z = s["zel"]
+    moe = {"kind": "moe", "expert": {"ff": z["expert_ff"]}, "shared": {"ff": z["shared_ff"]},
+           "router": {"experts": z["experts"], "top": z["top"], "scale": 2.0}}
+    par = {"left": {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["dim"], "vdim": z["vdim"],
+                    "scale": z["dim"] ** -0.5, "mask": {"size": z["window"]}, "rot": {"base": 1e6, "dims": z["rot_dims"]}},
+           "right": {"heads": z["s_heads"], "vdim": z["s_vdim"], "state": z["state"], "groups": z["groups"], "conv": z["conv"],
+                     "norm_groups": z["norm_groups"]}, "left_scale": 1.0, "right_scale": 1.0}
+    layers = []
+    for ch in z["pattern"]:
+        if ch == "g":
+            layers.append({"type": "general_delta", "mixer": {"heads": z["d_heads"], "dim": z["d_dim"]},
+                           "mlp": {"kind": "dense", "ff": s["ff"]}})
+        else:
+            layers.append({"type": "parallel", "mixer": dict(par), "mlp": dict(moe)})
+    a, b, t = z["loop"]
+    return {"architecture": "Zelinex", "vocab": s["vocab"], "width": s["width"], "norm": {"eps": 1e-5}, "residual_mult": 0.5,
+            "loop": {"start": a, "stop": b, "times": t}, "layers": layers}
+
+
 def _peaks(root):
     try:
         with open(os.path.join(root, "MEASURED_PEAKS.json")) as f:
@@ -124,8 +154,8 @@ def _cost(name, a, model, batch_info):
     """Algorithmic (bytes, flops, label) of one call from its arguments."""
     act = 2 if model.act == 0 else 4
     T, n_seq, ctx = batch_info
-    if name == "pieh_linear":
-        M, N, K, epi = a[9], a[10], a[11], a[12]
+    if name in ("pieh_linear", "pieh_linear_act"):
+        M, N, K, epi = a[9], a[10], a[11], a[12] if name == "pieh_linear" else 0
         ob = 4 if a[1] == 1 else 2
         wb = 4 if a[7] == 1 else 2
         extra = 2 * model.S * M * N * 4 if epi == 3 else M * N * ob
@@ -151,6 +181,28 @@ def _cost(name, a, model, batch_info):
         Tn, W, mix = a[6], a[7], a[2]
         parts = mix._obj.top if mix is not None else 0
         return Tn * W * 4 * (parts + 2 + (1 if a[3] is not None else 0)), 0.0, "residual_norm" + ("(mixture)" if parts else "")
+    if name == "pieh_sandwich_add":
+        Tn, W, mix = a[11], a[12], a[2]
+        parts = (mix._obj.top + 1) if mix is not None else (1 if a[1] is not None else 0)
+        adds = (1 if a[5] is not None else 0)
+        return (Tn * W * (4 * (parts + adds + 2) + (act if a[7] is not None else 0)), 0.0,
+                "sandwich_add" + ("(mixture)" if mix is not None else ""))
+    if name == "pieh_gated_group_norm":
+        return a[12] * a[7] * a[8] * (8 + act), 0.0, "gated_group_norm"
+    if name == "pieh_gdelta_prepare":
+        d = a[7]._obj
+        return a[8] * d.H * d.dk * 4 * 6, 0.0, "gdelta_prepare"
+    if name == "pieh_gdelta_scan":
+        d = a[6]._obj
+        return (n_seq * 2 * d.H * d.dk * d.dv * 4 + T * d.H * (5 * d.dk + 2 * d.dv) * 4, 8.0 * T * d.H * d.dk * d.dv,
+                "gdelta_scan")
+    if name in ("pieh_ssd_prepare", "pieh_ssd_scan"):
+        sd = a[4]._obj if name == "pieh_ssd_prepare" else a[3]._obj
+        Cn = sd.H * sd.P + 2 * sd.G * sd.N
+        if name == "pieh_ssd_prepare":
+            return T * (2 * Cn + 3 * sd.H) * 4, 2.0 * T * Cn * sd.taps, "ssd_prepare"
+        return (n_seq * 2 * sd.H * sd.N * sd.P * 4 + T * (Cn + sd.H * sd.P + 2 * sd.H) * 4, 5.0 * T * sd.H * sd.N * sd.P,
+                "ssd_scan")
     if name == "pieh_canon_conv":
         cn = a[0]._obj
         return T * a[3] * (4 + cn.n_out * act), 2.0 * T * a[3] * cn.n_out * cn.taps, "canon_conv"
@@ -231,7 +283,16 @@ def run(size="1b", prompt=4096, portion=4096, batch=4, steps=32, warmup=3, root=
 
     hbm, tfl, src = _peaks(root)
     t0 = time.time()
-    if family == "maginex":
+    if family == "zelinex":
+        from .zelinex import ZelinexArgs, ZelinexModel, random_weights
+        cfg = zelinex_config(size)
+        args = ZelinexArgs.from_dict(cfg)
+        weights = random_weights(args, seed=0, device="cuda")
+        n_params = sum(v.numel() for v in weights.values())
+        model = ZelinexModel(args, weights, "cuda", "bfloat16")
+        del weights
+        pattern = "".join(SIZES[size]["zel"]["pattern"][i] for i, _ in args.runs())
+    elif family == "maginex":
         from .maginex import MaginexArgs, MaginexModel, random_weights
         cfg = maginex_config(size)
         args = MaginexArgs.from_dict(cfg)
@@ -310,7 +371,10 @@ def run(size="1b", prompt=4096, portion=4096, batch=4, steps=32, warmup=3, root=
            "pipeline_error": int(timed._lib.pieh_pipeline_error()), "setup_s": round(time.time() - t0, 1)}
     del eng, model
     torch.cuda.empty_cache()
-    if family == "maginex":
+    if family == "zelinex":
+        if with_llama:      # the closest model of the framework (matrix-state recurrence + windowed attention) at the same sizes
+            out["golitar_equal_size"] = run(size, prompt, portion, batch, steps, warmup, root, with_llama=False)
+    elif family == "maginex":
         if with_llama:      # the closest model of the framework (sink attention + mixture of experts) at the same sizes
             out["babodra_equal_size"] = run(size, prompt, portion, batch, steps, warmup, root, with_llama=False,
                                             family="babodra")

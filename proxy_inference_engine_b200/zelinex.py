@@ -170,7 +170,7 @@ class ZelinexModel:
         self.act_torch = torch.float32 if self.exact else torch.bfloat16
         self.act = DTYPE_F32 if self.exact else DTYPE_BF16
         self.L = _lib.load_hybrid(build_if_missing=True)
-        self.W, W = args.width, args.width
+        self.W, W, self.S = args.width, args.width, 1        # one residual stream
         f32 = lambda t: t.to(device=device, dtype=torch.float32).contiguous()
         get = lambda name: weights[name]
         lin = lambda w, b=None: _Linear(w, b, self.exact, device)

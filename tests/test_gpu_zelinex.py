@@ -165,7 +165,7 @@ def test_sandwich_add_with_and_without_its_parts():
             assert float((h.double().cpu() - O.unit_rms(want, eps) * nw).abs().max()) < 1e-5
 
 
-@pytest.mark.parametrize("H,dk,dv", [(2, 16, 16), (3, 12, 20), (1, 40, 6), (2, 64, 64), (1, 130, 9)])
+@pytest.mark.parametrize("H,dk,dv", [(2, 16, 16), (3, 12, 20), (1, 40, 6), (2, 64, 64), (1, 130, 9), (2, 32, 40), (1, 128, 24), (2, 64, 7)])
 def test_generalized_delta_scan_with_states_in_slots(H, dk, dv):
     """Two sequences of unequal length in one step, then both continue from their slots (one of them a slot that held
     another sequence's state before)."""
@@ -222,7 +222,8 @@ def test_generalized_delta_prepare():
         assert float((got.double().cpu() - w_).abs().max()) < 1e-5
 
 
-@pytest.mark.parametrize("H,P,N,G,taps", [(4, 8, 12, 2, 3), (2, 6, 10, 1, 1), (3, 20, 33, 3, 4), (2, 64, 128, 1, 2), (6, 5, 7, 2, 8)])
+@pytest.mark.parametrize("H,P,N,G,taps", [(4, 8, 12, 2, 3), (2, 6, 10, 1, 1), (3, 20, 33, 3, 4), (2, 64, 128, 1, 2), (6, 5, 7, 2, 8),
+                                          (4, 8, 32, 2, 3), (2, 10, 16, 1, 2), (4, 3, 64, 4, 4), (3, 5, 64, 1, 2)])
 def test_state_space_prepare_and_scan_with_states_in_slots(H, P, N, G, taps):
     lib, L = _lib()
     inner, Cn = H * P, H * P + 2 * G * N
