@@ -151,26 +151,31 @@ __global__ void __launch_bounds__(kGdThreads) gdelta_scan_kernel(float* o, const
   }
 }
 
-// The same recurrence with the key size and the lanes per column fixed at compile time (DK = 16 R): a lane owns four runs of
-// four neighbouring state rows, so a token's five key-sized vectors arrive as 20 16-byte shared-memory loads with constant
-// offsets instead of 80 scalar ones with computed addresses, and nothing is predicated.  Needs every row start 16-byte aligned.
-template <int DK, int R>
-__global__ void __launch_bounds__(kGdThreads) gdelta_scan_fixed_kernel(float* o, const float* proj, long long ld,
-                                                                       const float* decay, const float* u, const float* au,
-                                                                       const pieh_gdelta d, const pieh_batch b) {
-  constexpr int RPT = DK / R, Q = RPT / 4, cols = kGdThreads / R, chunk = 16;
-  constexpr int tok_floats = 5 * DK, buf_floats = chunk * (tok_floats + cols);
-  static_assert(RPT % 4 == 0 && R <= 32 && (R & (R - 1)) == 0, "a lane owns whole runs of four rows");
+constexpr int kFixChunk = 16;   // tokens per shared-memory buffer of the fixed-size kernels
+
+// The same recurrence with the key size fixed at compile time.  A lane owns Q runs of four neighbouring state rows (R = DK / 4 Q
+// lanes per column), so a token's five key-sized vectors arrive as 5 Q 16-byte shared-memory loads with constant offsets and
+// nothing is predicated; a CTA is COLS columns wide (R COLS threads).  With few rows per lane a column's work is spread over
+// many warps: one sequence's heads then fill every scheduler with several warps whose shuffle and shared-memory latencies
+// overlap, where one warp per scheduler would sit out each of them.  Needs every row start 16-byte aligned.
+template <int DK, int Q, int COLS>
+__global__ void __launch_bounds__(DK / (4 * Q) * COLS) gdelta_scan_fixed_kernel(float* o, const float* proj, long long ld,
+                                                                                const float* decay, const float* u,
+                                                                                const float* au, const pieh_gdelta d,
+                                                                                const pieh_batch b) {
+  constexpr int R = DK / (4 * Q), NT = R * COLS, chunk = kFixChunk;
+  constexpr int tok_floats = 5 * DK, buf_floats = chunk * (tok_floats + COLS);
+  static_assert(R >= 1 && R <= 32 && (R & (R - 1)) == 0 && NT % 32 == 0, "the lanes of a column sit in one warp");
   extern __shared__ __align__(16) float sm[];
   pdl_sync();
   const int h = blockIdx.y, i = blockIdx.z;
   const int start = b.seq_start[i], n = b.seq_len[i], ctx = b.seq_ctx[i];
   const int rl = threadIdx.x % R, cl = threadIdx.x / R;
-  const int j = blockIdx.x * cols + cl;           // column of S (feature of v)
+  const int j = blockIdx.x * COLS + cl;           // column of S (feature of v)
   const int dv = d.dv;
   const bool col_ok = j < dv;
   float* S_g = d.state + (((size_t)b.seq_slot[i] * d.H + h) * DK) * dv;
-  float S[RPT];   // S[4 q + e] is state row q * 4 R + 4 rl + e
+  float S[4 * Q];   // S[4 q + e] is state row q * 4 R + 4 rl + e
 #pragma unroll
   for (int q = 0; q < Q; ++q)
 #pragma unroll
@@ -181,7 +186,7 @@ __global__ void __launch_bounds__(kGdThreads) gdelta_scan_fixed_kernel(float* o,
     float* vs = base + chunk * tok_floats;
     const int nc = min(chunk, n - c0);
     constexpr int per = DK / 4;
-    for (int e = threadIdx.x; e < nc * per; e += kGdThreads) {
+    for (int e = threadIdx.x; e < nc * per; e += NT) {
       const int tt = e / per, r = (e - tt * per) * 4;
       const size_t row = (size_t)(start + c0 + tt);
       const size_t s3 = (row * d.H + h) * DK + r;
@@ -192,9 +197,9 @@ __global__ void __launch_bounds__(kGdThreads) gdelta_scan_fixed_kernel(float* o,
       gd_cp_async(dst + 3 * DK, proj + row * ld + d.k_off + (size_t)h * DK + r, 16);
       gd_cp_async(dst + 4 * DK, proj + row * ld + d.r_off + (size_t)h * DK + r, 16);
     }
-    for (int e = threadIdx.x; e < nc * cols; e += kGdThreads) {
-      const int tt = e / cols, c = e - tt * cols;
-      const int jj = min(blockIdx.x * cols + c, dv - 1);
+    for (int e = threadIdx.x; e < nc * COLS; e += NT) {
+      const int tt = e / COLS, c = e - tt * COLS;
+      const int jj = min(blockIdx.x * COLS + c, dv - 1);
       gd_cp_async(vs + e, proj + (size_t)(start + c0 + tt) * ld + d.v_off + (size_t)h * dv + jj, 4);
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
@@ -229,13 +234,14 @@ __global__ void __launch_bounds__(kGdThreads) gdelta_scan_fixed_kernel(float* o,
       float p = pp[0];
 #pragma unroll
       for (int q = 1; q < Q; ++q) p += pp[q];
+      // the read-out of the PREVIOUS token is reduced over the R lanes together with this token's projection
 #pragma unroll
       for (int off = 1; off < R; off <<= 1) {
         p += __shfl_xor_sync(0xffffffffu, p, off);
         out_prev += __shfl_xor_sync(0xffffffffu, out_prev, off);
       }
       if (row_prev >= 0 && rl == 0 && col_ok) o[((size_t)row_prev * d.H + h) * dv + j] = out_prev;
-      const float vj = vs[tt * cols + cl];
+      const float vj = vs[tt * COLS + cl];
       float oo[Q];
 #pragma unroll
       for (int q = 0; q < Q; ++q) {
@@ -263,17 +269,17 @@ __global__ void __launch_bounds__(kGdThreads) gdelta_scan_fixed_kernel(float* o,
   }
 }
 
-template <int DK, int R>
+template <int DK, int Q, int COLS>
 static cudaError_t launch_gdelta_fixed(float* o, const float* proj, long long ld, const float* decay, const float* u,
                                        const float* au, const pieh_gdelta& d, const pieh_batch& b, cudaStream_t st) {
-  constexpr int cols = kGdThreads / R;
-  constexpr size_t smem = (size_t)2 * 16 * (5 * DK + cols) * 4;
+  constexpr int NT = DK / (4 * Q) * COLS;
+  constexpr size_t smem = (size_t)2 * kFixChunk * (5 * DK + COLS) * 4;
   static bool opted = false;
   if (smem > 48 * 1024 && !opted) {
-    cudaFuncSetAttribute(gdelta_scan_fixed_kernel<DK, R>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaFuncSetAttribute(gdelta_scan_fixed_kernel<DK, Q, COLS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     opted = true;
   }
-  return launch_k(gdelta_scan_fixed_kernel<DK, R>, dim3((d.dv + cols - 1) / cols, d.H, b.n_seq), dim3(kGdThreads), smem, st, o,
+  return launch_k(gdelta_scan_fixed_kernel<DK, Q, COLS>, dim3((d.dv + COLS - 1) / COLS, d.H, b.n_seq), dim3(NT), smem, st, o,
                   proj, ld, decay, u, au, d, b);
 }
 
@@ -308,9 +314,11 @@ extern "C" int pieh_gdelta_scan(float* o, const float* proj, long long ld, const
   if (aligned && !generic_only && (d->dk == 32 || d->dk == 64 || d->dk == 128)) {
     count_launch();
     cudaStream_t st = (cudaStream_t)stream;
-    return status_of(d->dk == 32 ? launch_gdelta_fixed<32, 2>(o, proj, ld, decay, u, au, *d, *b, st)
-                     : d->dk == 64 ? launch_gdelta_fixed<64, 4>(o, proj, ld, decay, u, au, *d, *b, st)
-                                   : launch_gdelta_fixed<128, 8>(o, proj, ld, decay, u, au, *d, *b, st));
+    // measured at dk = dv = 128, 16 heads, one 4096-row portion: 4 / 8 / 16 rows per lane 1.35 / 1.18 / 1.24 ms
+    if (d->dk == 128) return status_of(launch_gdelta_fixed<128, 2, 16>(o, proj, ld, decay, u, au, *d, *b, st));
+    return status_of(d->dk == 32 ? launch_gdelta_fixed<32, 1, 16>(o, proj, ld, decay, u, au, *d, *b, st)
+                     : d->dk == 64 ? launch_gdelta_fixed<64, 1, 16>(o, proj, ld, decay, u, au, *d, *b, st)
+                                   : launch_gdelta_fixed<128, 1, 16>(o, proj, ld, decay, u, au, *d, *b, st));
   }
   constexpr int RPT = 16;            // rows of a state column per lane
   int R = 1;

@@ -168,27 +168,31 @@ __global__ void __launch_bounds__(kSsdThreads) ssd_scan_kernel(float* y, const f
   }
 }
 
-// The same recurrence with the state size and the lanes per column fixed at compile time (N = 16 R): a lane owns four runs
-// of four neighbouring state rows, so B and C of a token arrive as 8 16-byte shared-memory loads with constant offsets.
-template <int N, int R>
-__global__ void __launch_bounds__(kSsdThreads) ssd_scan_fixed_kernel(float* y, const float* xbc, const float* dtd,
-                                                                     const pieh_ssd s, const pieh_batch b) {
-  constexpr int RPT = N / R, Q = RPT / 4, cols = kSsdThreads / R;
-  constexpr int buf_floats = kSsdChunk * (2 * N + cols + 2);
-  static_assert(RPT % 4 == 0 && R <= 32 && (R & (R - 1)) == 0, "a lane owns whole runs of four rows");
+// The same recurrence with the state size fixed at compile time.  A lane owns Q runs of four neighbouring state rows (R =
+// N / 4 Q lanes per column), so B and C of a token arrive as 2 Q 16-byte shared-memory loads with constant offsets; a CTA is
+// COLS columns wide (R COLS threads).  Nothing in a token's update waits for a reduction, so few rows per lane and many
+// warps per scheduler is the fast shape: the deferred read-out shuffles of one warp hide behind the others' arithmetic.
+constexpr int kFixChunk = 16;   // tokens per shared-memory buffer of the fixed-size kernels
+
+template <int N, int Q, int COLS>
+__global__ void __launch_bounds__(N / (4 * Q) * COLS) ssd_scan_fixed_kernel(float* y, const float* xbc, const float* dtd,
+                                                                            const pieh_ssd s, const pieh_batch b) {
+  constexpr int R = N / (4 * Q), NT = R * COLS;
+  constexpr int buf_floats = kFixChunk * (2 * N + COLS + 2);
+  static_assert(R >= 1 && R <= 32 && (R & (R - 1)) == 0 && NT % 32 == 0, "the lanes of a column sit in one warp");
   extern __shared__ __align__(16) float sm[];
   pdl_sync();
   const int h = blockIdx.y, i = blockIdx.z;
   const int g = h / (s.H / s.G);
   const int start = b.seq_start[i], n = b.seq_len[i], ctx = b.seq_ctx[i];
   const int rl = threadIdx.x % R, cl = threadIdx.x / R;
-  const int j = blockIdx.x * cols + cl;
+  const int j = blockIdx.x * COLS + cl;
   const int P = s.P;
   const bool col_ok = j < P;
   const int C = s.H * P + 2 * s.G * N;
   const int offB = s.H * P + g * N, offC = s.H * P + s.G * N + g * N;
   float* S_g = s.state + (((size_t)b.seq_slot[i] * s.H + h) * N) * P;
-  float S[RPT];   // S[4 q + e] is state row q * 4 R + 4 rl + e
+  float S[4 * Q];   // S[4 q + e] is state row q * 4 R + 4 rl + e
 #pragma unroll
   for (int q = 0; q < Q; ++q)
 #pragma unroll
@@ -197,72 +201,75 @@ __global__ void __launch_bounds__(kSsdThreads) ssd_scan_fixed_kernel(float* y, c
   const float Dh = s.D ? s.D[h] : 0.f;
   auto fill = [&](int which, int c0) {
     float* bc = sm + which * buf_floats;
-    float* xs = bc + kSsdChunk * 2 * N;
-    float* sc = xs + kSsdChunk * cols;
-    const int nc = min(kSsdChunk, n - c0);
+    float* xs = bc + kFixChunk * 2 * N;
+    float* sc = xs + kFixChunk * COLS;
+    const int nc = min(kFixChunk, n - c0);
     constexpr int per = N / 4;
-    for (int e = threadIdx.x; e < nc * per; e += kSsdThreads) {
+    for (int e = threadIdx.x; e < nc * per; e += NT) {
       const int tt = e / per, r = (e - tt * per) * 4;
       const float* row = xbc + (size_t)(start + c0 + tt) * C;
       ssd_cp_async(bc + tt * 2 * N + r, row + offB + r, 16);
       ssd_cp_async(bc + tt * 2 * N + N + r, row + offC + r, 16);
     }
-    for (int e = threadIdx.x; e < nc * cols; e += kSsdThreads) {
-      const int tt = e / cols, c = e - tt * cols;
-      const int jj = min(blockIdx.x * cols + c, P - 1);
+    for (int e = threadIdx.x; e < nc * COLS; e += NT) {
+      const int tt = e / COLS, c = e - tt * COLS;
+      const int jj = min(blockIdx.x * COLS + c, P - 1);
       ssd_cp_async(xs + e, xbc + (size_t)(start + c0 + tt) * C + (size_t)h * P + jj, 4);
     }
-    for (int e = threadIdx.x; e < nc * 2; e += kSsdThreads)
+    for (int e = threadIdx.x; e < nc * 2; e += NT)
       ssd_cp_async(sc + e, dtd + ((size_t)(start + c0 + (e >> 1)) * s.H + h) * 2 + (e & 1), 4);
     asm volatile("cp.async.commit_group;" ::: "memory");
   };
-  float out_prev = 0.f, skip_prev = 0.f;
-  int row_prev = -1;
   fill(0, 0);
-  for (int c0 = 0, which = 0; c0 < n; c0 += kSsdChunk, which ^= 1) {
-    const int nc = min(kSsdChunk, n - c0);
-    if (c0 + kSsdChunk < n) {
-      fill(which ^ 1, c0 + kSsdChunk);
+  for (int c0 = 0, which = 0; c0 < n; c0 += kFixChunk, which ^= 1) {
+    const int nc = min(kFixChunk, n - c0);
+    if (c0 + kFixChunk < n) {
+      fill(which ^ 1, c0 + kFixChunk);
       asm volatile("cp.async.wait_group 1;" ::: "memory");
     } else {
       asm volatile("cp.async.wait_group 0;" ::: "memory");
     }
     __syncthreads();
     const float* bc = sm + which * buf_floats;
-    const float* xs = bc + kSsdChunk * 2 * N;
-    const float* sc = xs + kSsdChunk * cols;
-#pragma unroll 4
-    for (int tt = 0; tt < nc; ++tt) {
-      const float4* t4 = reinterpret_cast<const float4*>(bc + tt * 2 * N) + rl;
-      float4 Bv[Q], Cv[Q];
+    const float* xs = bc + kFixChunk * 2 * N;
+    const float* sc = xs + kFixChunk * COLS;
+    // four tokens at a time: their read-outs are summed over the R lanes as four independent shuffle chains, so a chain's
+    // latency is paid once per four tokens (the state update itself never waits for a reduction)
+    for (int t0 = 0; t0 < nc; t0 += 4) {
+      float part[4], skip[4];
 #pragma unroll
-      for (int q = 0; q < Q; ++q) { Bv[q] = t4[q * R]; Cv[q] = t4[N / 4 + q * R]; }
+      for (int k = 0; k < 4; ++k) {
+        part[k] = 0.f; skip[k] = 0.f;
+        const int tt = t0 + k;
+        if (tt < nc) {
+          const float4* t4 = reinterpret_cast<const float4*>(bc + tt * 2 * N) + rl;
+          const float dt = sc[2 * tt], dec = sc[2 * tt + 1];
+          const float xj = xs[tt * COLS + cl];
+          const float dx = dt * xj;
 #pragma unroll
-      for (int off = 1; off < R; off <<= 1) out_prev += __shfl_xor_sync(0xffffffffu, out_prev, off);
-      if (row_prev >= 0 && rl == 0 && col_ok) y[((size_t)row_prev * s.H + h) * P + j] = out_prev + skip_prev;
-      const float dt = sc[2 * tt], dec = sc[2 * tt + 1];
-      const float xj = xs[tt * cols + cl];
-      const float dx = dt * xj;
-      float oo[Q];
-#pragma unroll
-      for (int q = 0; q < Q; ++q) {
-        S[4 * q] = fmaf(dec, S[4 * q], dx * Bv[q].x);
-        S[4 * q + 1] = fmaf(dec, S[4 * q + 1], dx * Bv[q].y);
-        S[4 * q + 2] = fmaf(dec, S[4 * q + 2], dx * Bv[q].z);
-        S[4 * q + 3] = fmaf(dec, S[4 * q + 3], dx * Bv[q].w);
-        oo[q] = fmaf(S[4 * q + 3], Cv[q].w, fmaf(S[4 * q + 2], Cv[q].z, fmaf(S[4 * q + 1], Cv[q].y, S[4 * q] * Cv[q].x)));
+          for (int q = 0; q < Q; ++q) {
+            const float4 Bv = t4[q * R], Cv = t4[N / 4 + q * R];
+            S[4 * q] = fmaf(dec, S[4 * q], dx * Bv.x);
+            S[4 * q + 1] = fmaf(dec, S[4 * q + 1], dx * Bv.y);
+            S[4 * q + 2] = fmaf(dec, S[4 * q + 2], dx * Bv.z);
+            S[4 * q + 3] = fmaf(dec, S[4 * q + 3], dx * Bv.w);
+            part[k] += fmaf(S[4 * q + 3], Cv.w, fmaf(S[4 * q + 2], Cv.z, fmaf(S[4 * q + 1], Cv.y, S[4 * q] * Cv.x)));
+          }
+          skip[k] = Dh * xj;
+        }
       }
-      out_prev = oo[0];
 #pragma unroll
-      for (int q = 1; q < Q; ++q) out_prev += oo[q];
-      skip_prev = Dh * xj;
-      row_prev = start + c0 + tt;
+      for (int off = 1; off < R; off <<= 1)
+#pragma unroll
+        for (int k = 0; k < 4; ++k) part[k] += __shfl_xor_sync(0xffffffffu, part[k], off);
+      if (rl == 0 && col_ok) {
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          if (t0 + k < nc) y[((size_t)(start + c0 + t0 + k) * s.H + h) * P + j] = part[k] + skip[k];
+      }
     }
     __syncthreads();
   }
-#pragma unroll
-  for (int off = 1; off < R; off <<= 1) out_prev += __shfl_xor_sync(0xffffffffu, out_prev, off);
-  if (row_prev >= 0 && rl == 0 && col_ok) y[((size_t)row_prev * s.H + h) * P + j] = out_prev + skip_prev;
   if (col_ok) {
 #pragma unroll
     for (int q = 0; q < Q; ++q)
@@ -271,12 +278,17 @@ __global__ void __launch_bounds__(kSsdThreads) ssd_scan_fixed_kernel(float* y, c
   }
 }
 
-template <int N, int R>
+template <int N, int Q, int COLS>
 static cudaError_t launch_ssd_fixed(float* y, const float* xbc, const float* dtd, const pieh_ssd& s, const pieh_batch& b,
                                     cudaStream_t st) {
-  constexpr int cols = kSsdThreads / R;
-  constexpr size_t smem = (size_t)2 * kSsdChunk * (2 * N + cols + 2) * 4;
-  return launch_k(ssd_scan_fixed_kernel<N, R>, dim3((s.P + cols - 1) / cols, s.H, b.n_seq), dim3(kSsdThreads), smem, st, y, xbc,
+  constexpr int NT = N / (4 * Q) * COLS;
+  constexpr size_t smem = (size_t)2 * kFixChunk * (2 * N + COLS + 2) * 4;
+  static bool opted = false;
+  if (smem > 48 * 1024 && !opted) {
+    cudaFuncSetAttribute(ssd_scan_fixed_kernel<N, Q, COLS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    opted = true;
+  }
+  return launch_k(ssd_scan_fixed_kernel<N, Q, COLS>, dim3((s.P + COLS - 1) / COLS, s.H, b.n_seq), dim3(NT), smem, st, y, xbc,
                   dtd, s, b);
 }
 
@@ -315,10 +327,12 @@ extern "C" int pieh_ssd_scan(float* y, const float* xbc, const float* dtd, const
   if (aligned && !generic_only && (s->N == 16 || s->N == 32 || s->N == 64 || s->N == 128)) {
     count_launch();
     cudaStream_t st = (cudaStream_t)stream;
-    return status_of(s->N == 16 ? launch_ssd_fixed<16, 1>(y, xbc, dtd, *s, *b, st)
-                     : s->N == 32 ? launch_ssd_fixed<32, 2>(y, xbc, dtd, *s, *b, st)
-                     : s->N == 64 ? launch_ssd_fixed<64, 4>(y, xbc, dtd, *s, *b, st)
-                                  : launch_ssd_fixed<128, 8>(y, xbc, dtd, *s, *b, st));
+    // measured at N = 128, P = 64, 32 heads, one 4096-row portion: 4 / 8 / 16 rows per lane 0.81 / 0.64 / 0.70 ms
+    if (s->N == 128) return status_of(launch_ssd_fixed<128, 2, 16>(y, xbc, dtd, *s, *b, st));
+    return status_of(s->N == 16 ? launch_ssd_fixed<16, 1, 32>(y, xbc, dtd, *s, *b, st)
+                     : s->N == 32 ? launch_ssd_fixed<32, 1, 16>(y, xbc, dtd, *s, *b, st)
+                     : s->N == 64 ? launch_ssd_fixed<64, 1, 16>(y, xbc, dtd, *s, *b, st)
+                                  : launch_ssd_fixed<128, 1, 16>(y, xbc, dtd, *s, *b, st));
   }
   constexpr int RPT = 16;            // rows of a state column per lane
   int R = 1;
