@@ -380,8 +380,9 @@ __global__ void __launch_bounds__(128) bias_tile_kernel(__nv_bfloat16* out, cons
     if (sgm) {
 #pragma unroll
       for (int n = 0; n < NT; ++n) {   // a masked score is -inf: exp2(+inf) = inf and the weight is exactly 0
-        pf[n][0] = pack2(1.f / (1.f + exp2f(-(s[n][0] + sb2))), 1.f / (1.f + exp2f(-(s[n][1] + sb2))));
-        pf[n][1] = pack2(1.f / (1.f + exp2f(-(s[n][2] + sb2))), 1.f / (1.f + exp2f(-(s[n][3] + sb2))));
+        // the weights are rounded to bf16 for the tensor cores right away: the fast division (2 ulp) is exact enough
+        pf[n][0] = pack2(__fdividef(1.f, 1.f + exp2f(-(s[n][0] + sb2))), __fdividef(1.f, 1.f + exp2f(-(s[n][1] + sb2))));
+        pf[n][1] = pack2(__fdividef(1.f, 1.f + exp2f(-(s[n][2] + sb2))), __fdividef(1.f, 1.f + exp2f(-(s[n][3] + sb2))));
       }
     } else {
     mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1)); mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
